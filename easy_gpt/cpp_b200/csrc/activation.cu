@@ -74,3 +74,49 @@ EG_API int eg_swiglu(cudaStream_t stream, int dtype, const void* gate_up, int ld
         swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gate_up, ld, (float*)out, ldo, inter);
     return eg_launch_status();
 }
+
+// Two more activations between the products of a feed-forward, element by element in float32:
+//   eg_squared_relu   out[t, c] = max(x[t, c], 0)^2
+//   eg_clamped_glu    on interleaved columns (gate_0, up_0, gate_1, up_1, ...): g = min(gate, limit), u = clamp(up, -limit, limit),
+//                     out[t, i] = g * sigmoid(1.702 g) * (u + 1)
+template <typename TI, typename TO>
+__global__ void squared_relu_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int tokens, int n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * n) return;
+    const int t = (int)(i / n), c = (int)(i % n);
+    const float z = fmaxf(to_f32<TI>(x[(size_t)t * ldx + c]), 0.f);
+    out[(size_t)t * ldo + c] = from_f32<TO>(z * z);
+}
+
+template <typename TI, typename TO>
+__global__ void clamped_glu_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int tokens, int n, float limit) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * n) return;
+    const int t = (int)(i / n), c = (int)(i % n);
+    const float g = fminf(to_f32<TI>(x[(size_t)t * ldx + 2 * c]), limit);
+    const float u = fminf(fmaxf(to_f32<TI>(x[(size_t)t * ldx + 2 * c + 1]), -limit), limit);
+    out[(size_t)t * ldo + c] = from_f32<TO>(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+}
+
+EG_API int eg_squared_relu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n) {
+    const long long total = (long long)tokens * n;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (x_dtype == EG_F32 && out_dtype == EG_F32) squared_relu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (float*)out, ldo, tokens, n);
+    else if (x_dtype == EG_F32) squared_relu_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (bf16*)out, ldo, tokens, n);
+    else if (out_dtype == EG_F32) squared_relu_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (float*)out, ldo, tokens, n);
+    else squared_relu_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (bf16*)out, ldo, tokens, n);
+    return eg_launch_status();
+}
+
+// x [tokens, 2 n] interleaved -> out [tokens, n]
+EG_API int eg_clamped_glu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float limit) {
+    const long long total = (long long)tokens * n;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (x_dtype == EG_F32 && out_dtype == EG_F32) clamped_glu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (float*)out, ldo, tokens, n, limit);
+    else if (x_dtype == EG_F32) clamped_glu_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (bf16*)out, ldo, tokens, n, limit);
+    else if (out_dtype == EG_F32) clamped_glu_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (float*)out, ldo, tokens, n, limit);
+    else clamped_glu_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (bf16*)out, ldo, tokens, n, limit);
+    return eg_launch_status();
+}

@@ -1,0 +1,137 @@
+// A causal convolution over time in front of a mixer, on the normed rows of the stream, channel by channel:
+//
+//   h[t]   = gain * x[t] / sqrt(mean(x[t]^2) + eps)                      (the norm in front, computed here from the float32 stream)
+//   out[t] = h[t] + sum_{j < taps} w[:, j] * h[t - taps + 1 + j]         rows before the request's start are zero
+//
+// The last taps - 1 normed rows of a request are its state (float32, [taps - 1, hidden] in the request's slot, oldest
+// first), so that a step continues where the one before ended.  Two kernels: the first reads the slots and writes both
+// h (for a part that reads the plain norm) and out; the second, launched behind it, moves the slots on.  A row's norm is
+// computed by the same instructions whether the row is a token's own or an earlier one, and the slot keeps float32
+// values: a cut between two steps changes nothing.
+//
+//   eg_rmsnorm_conv_shift        both outputs from the stream (gain [hidden]; plain_out may be null)
+//   eg_conv_shift                the same from rows that are normed already (float32)
+//   eg_conv_shift_state          the slots of every entry move on by the entry's rows
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_TAPS = 8;
+
+// NORMED: `rows` are h already; else they are the stream and h is computed here
+template <typename TO, bool NORMED>
+__global__ void conv_shift_kernel(const float* __restrict__ rows, const float* __restrict__ gain, float eps, const float* __restrict__ w,
+                                  const float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
+                                  const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, TO* __restrict__ out, TO* __restrict__ plain_out,
+                                  int hidden, int taps) {
+    __shared__ float scratch[32];
+    __shared__ float inv[MAX_TAPS];
+    const int t = blockIdx.x, seq = token_seq[t], start = seq_starts[seq];
+    const int back = min(taps - 1, t - start);                  // earlier rows that lie in this step
+    const float* slot = state + (size_t)seq_slots[seq] * slot_floats;
+    for (int d = 0; d <= back; ++d) {
+        float r = 1.0f;
+        if (!NORMED) {
+            const float* x = rows + (size_t)(t - d) * hidden;
+            float ss = 0.f;
+            for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
+            ss = block_sum(ss, scratch);
+            r = 1.0f / sqrtf(ss / (float)hidden + eps);
+        }
+        if (threadIdx.x == 0) inv[d] = r;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float g = NORMED ? 1.0f : gain[j];
+        float own = 0.f, acc = 0.f;
+        // tap k weighs the row d = taps - 1 - k tokens back; oldest first, so that the sum's order is the same everywhere
+        for (int k = 0; k < taps; ++k) {
+            const int d = taps - 1 - k;
+            float v;
+            if (d <= back) {
+                const float xv = rows[(size_t)(t - d) * hidden + j];
+                v = NORMED ? xv : g * (xv * inv[d]);
+            } else {
+                // d - back - 1 rows before the step's first: the slot's row (taps - 1) - (d - back)
+                v = slot[(size_t)(taps - 1 - (d - back)) * hidden + j];
+            }
+            if (d == 0) own = v;
+            acc = fmaf(w[(size_t)j * taps + k], v, acc);
+        }
+        out[(size_t)t * hidden + j] = from_f32<TO>(own + acc);
+        if (plain_out) plain_out[(size_t)t * hidden + j] = from_f32<TO>(own);
+    }
+}
+
+// one block per entry; a thread owns its channels in every row of the slot, so the rows can move in place
+template <bool NORMED>
+__global__ void conv_shift_state_kernel(const float* __restrict__ rows, const float* __restrict__ gain, float eps, float* __restrict__ state,
+                                        long long slot_floats, const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, int hidden, int taps) {
+    __shared__ float scratch[32];
+    __shared__ float inv[MAX_TAPS];
+    const int seq = blockIdx.x, start = seq_starts[seq], len = seq_starts[seq + 1] - start;
+    if (len <= 0) return;
+    float* slot = state + (size_t)seq_slots[seq] * slot_floats;
+    const int keep = taps - 1;
+    const int fresh = min(keep, len);                           // the slot's last `fresh` rows come from this step
+    for (int r = 0; r < fresh; ++r) {
+        float v = 1.0f;
+        if (!NORMED) {
+            const float* x = rows + (size_t)(start + len - fresh + r) * hidden;
+            float ss = 0.f;
+            for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
+            ss = block_sum(ss, scratch);
+            v = 1.0f / sqrtf(ss / (float)hidden + eps);
+        }
+        if (threadIdx.x == 0) inv[r] = v;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        for (int r = 0; r < keep - fresh; ++r) slot[(size_t)r * hidden + j] = slot[(size_t)(r + fresh) * hidden + j];
+        for (int r = 0; r < fresh; ++r) {
+            const float xv = rows[(size_t)(start + len - fresh + r) * hidden + j];
+            slot[(size_t)(keep - fresh + r) * hidden + j] = NORMED ? xv : gain[j] * (xv * inv[r]);
+        }
+    }
+}
+
+template <bool NORMED>
+int launch_conv_shift(cudaStream_t stream, const float* rows, const float* gain, float eps, const float* w, const float* state, long long slot_floats,
+                      const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out, int out_dtype, int tokens, int hidden,
+                      int taps) {
+    if (tokens <= 0) return 0;
+    if (taps < 1 || taps > MAX_TAPS || hidden <= 0 || (taps > 1 && slot_floats < (long long)(taps - 1) * hidden)) return (int)cudaErrorInvalidValue;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (out_dtype == EG_BF16)
+        conv_shift_kernel<bf16, NORMED><<<tokens, threads, 0, stream>>>(rows, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, (bf16*)out,
+                                                                       (bf16*)plain_out, hidden, taps);
+    else
+        conv_shift_kernel<float, NORMED><<<tokens, threads, 0, stream>>>(rows, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, (float*)out,
+                                                                        (float*)plain_out, hidden, taps);
+    return eg_launch_status();
+}
+}  // namespace
+
+// stream float32 [tokens, hidden]; w float32 [hidden, taps] (the last tap weighs the token's own row); state float32
+// [slots, slot_floats] with this part's (taps - 1) * hidden values first; out and plain_out [tokens, hidden] in out_dtype
+EG_API int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, const float* state,
+                                 long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out,
+                                 int out_dtype, int tokens, int hidden, int taps) {
+    return launch_conv_shift<false>(stream, residual, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, out, plain_out, out_dtype, tokens, hidden,
+                                    taps);
+}
+
+EG_API int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, const float* state, long long slot_floats, const int* token_seq,
+                         const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps) {
+    return launch_conv_shift<true>(stream, rows, nullptr, 0.f, w, state, slot_floats, token_seq, seq_starts, seq_slots, out, nullptr, out_dtype, tokens, hidden, taps);
+}
+
+// gain null: `rows` are normed already; else they are the stream and the slot receives gain * x / rms(x)
+EG_API int eg_conv_shift_state(cudaStream_t stream, const float* rows, const float* gain, float eps, float* state, long long slot_floats, const int* seq_starts,
+                               const int* seq_slots, int num_seqs, int hidden, int taps) {
+    if (num_seqs <= 0 || taps <= 1) return 0;
+    if (taps > MAX_TAPS || slot_floats < (long long)(taps - 1) * hidden) return (int)cudaErrorInvalidValue;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (gain) conv_shift_state_kernel<false><<<num_seqs, threads, 0, stream>>>(rows, gain, eps, state, slot_floats, seq_starts, seq_slots, hidden, taps);
+    else conv_shift_state_kernel<true><<<num_seqs, threads, 0, stream>>>(rows, nullptr, 0.f, state, slot_floats, seq_starts, seq_slots, hidden, taps);
+    return eg_launch_status();
+}

@@ -430,6 +430,126 @@ inline ModelSpec lasizen_spec(const json::Value& config) {
     return spec;
 }
 
+// ---- Masezen ---------------------------------------------------------------------------------------------------------------
+// A decoder whose config.json lists its layers one by one.  A layer has ONE norm (an RMS norm whose gain is a single number)
+// that both branches read, side by side:  h = n(x);  x = x + s1 * mixer(h + conv(h)) + s2 * ff(h),  with conv a causal
+// convolution over time on each channel (canon.taps taps, the last taps - 1 rows of h kept per request), s1 and s2 a gain
+// per channel; behind it every layer adds a small gated map of a per-token vector (token_side.dim columns of a table that
+// all layers share) through an RMS norm of its own.  The mixer ("type": "attention") is grouped-query attention whose
+// values are the keys as projected, with normed and turned queries and keys, scores mixed across the heads and a gated
+// output.  "mlp" is null, a dense feed-forward with a squared ReLU, or routed experts with a clamped gate whose weights
+// multiply the experts' inputs, beside a shared expert.  Every size and constant is a key of config.json; tensor names are
+// "l<i>.<part>.<tensor>".
+inline ModelSpec masezen_spec(const json::Value& config) {
+    using C = GufanexConfig;
+    if (!config.is_object()) throw ConfigError("config.json is not a JSON object");
+    ModelSpec spec;
+    spec.architecture = "masezen";
+    const long long width = C::integer(config, "width", ""), vocab = C::integer(config, "vocab", "");
+    if (width <= 0 || vocab <= 0) throw ConfigError("width and vocab must be > 0");
+    const double eps = C::number(C::need(config, "norm", ""), "eps", "norm.");
+    if (eps <= 0.0) throw ConfigError("norm.eps must be > 0");
+    spec.vocab_size = vocab;
+    spec.hidden_size = width;
+    spec.max_positions = C::integer_or(config, "max_positions", 1LL << 30, "");
+    auto single_norm = [&](const std::string& name) {
+        return PartSpec{"rmsnorm", Params{{"size", width}, {"eps", eps}, {"weight_name", ""}, {"single_gain", 1}}, name, true};
+    };
+    const long long taps = C::present(config, "canon") ? C::integer(*config.find("canon"), "taps", "canon.") : 0;
+    if (taps < 0 || taps > 8) throw ConfigError("canon.taps must lie in 1..8");
+    const long long side = C::present(config, "token_side") ? C::integer(*config.find("token_side"), "dim", "token_side.") : 0;
+    if (side < 0) throw ConfigError("token_side.dim must be > 0");
+    const json::Value& layers = C::need(config, "layers", "");
+    if (!layers.is_array() || layers.array.empty()) throw ConfigError("layers must be a list with at least one layer");
+    const long long count = (long long)layers.array.size();
+    for (size_t i = 0; i < layers.array.size(); ++i) {
+        const json::Value& l = layers.array[i];
+        const std::string where = "layers[" + std::to_string(i) + "].", prefix = "l" + std::to_string(i), w = where + "mixer.";
+        const json::Value& type = C::need(l, "type", where);
+        const json::Value& m = C::need(l, "mixer", where);
+        if (!type.is_string() || type.string != "attention") throw ConfigError(where + "type must be 'attention', the mixer of this design");
+        LayerSpec layer;
+        layer.parallel = true;
+        const long long heads = C::integer(m, "heads", w), kv_heads = C::integer(m, "kv_heads", w), dim = C::integer(m, "dim", w);
+        if (heads <= 0 || kv_heads <= 0 || dim <= 0 || heads % kv_heads) throw ConfigError(w + "heads, kv_heads and dim must be > 0, heads a multiple of kv_heads");
+        if (C::present(m, "vdim") && C::integer(m, "vdim", w) != dim) throw ConfigError(w + "vdim must equal dim: the values are the keys");
+        PartSpec mixer{"mixed_attention", Params{{"hidden_size", width}, {"heads", heads}, {"kv_heads", kv_heads}, {"dim", dim}, {"scale", C::number(m, "scale", w)},
+                                                 {"norm_eps", eps}}, prefix + ".mix", true};
+        if (C::present(m, "rot")) {
+            const json::Value& rot = *m.find("rot");
+            const long long dims = C::integer(rot, "dims", w + "rot.");
+            if (dims < 0 || dims % 2 || dims > dim) throw ConfigError(w + "rot.dims must be even and within dim");
+            if (dims > 0) {
+                Params r{{"head_dim", dim}, {"rotary_dim", dims}, {"theta", C::number(rot, "base", w + "rot.")}};
+                if (C::present(rot, "scaling")) {
+                    const json::Value& sc = *rot.find("scaling");
+                    const std::string ws = w + "rot.scaling.";
+                    r.set("scaling_factor", C::number(sc, "factor", ws));
+                    r.set("scaling_original", C::number(sc, "original", ws));
+                    r.set("scaling_fast", C::number(sc, "fast", ws));
+                    r.set("scaling_slow", C::number(sc, "slow", ws));
+                }
+                layer.position = PartSpec{"rope", r, "", true};
+            }
+        }
+        auto gain = [&](const std::string& name) { return PartSpec{"layer_scale", Params{{"size", width}, {"weight_name", ""}}, name, true}; };
+        SubLayerSpec mix{"mixer", mixer, single_norm(prefix + ".norm1"), "pre", gain(prefix + ".ls1")};
+        if (taps > 0) mix.shift = PartSpec{"conv_shift", Params{{"size", width}, {"taps", taps}}, prefix + ".canon1", true};
+        layer.sublayers.push_back(std::move(mix));
+        if (C::present(l, "mlp")) {
+            const json::Value& mlp = *l.find("mlp");
+            const std::string wm = where + "mlp.";
+            const json::Value& kind = C::need(mlp, "kind", wm);
+            if (!kind.is_string()) throw ConfigError(wm + "kind must be a string");
+            PartSpec ff;
+            if (kind.string == "dense") {
+                const long long f = C::integer(mlp, "ff", wm);
+                if (f <= 0) throw ConfigError(wm + "ff must be > 0");
+                ff = PartSpec{"squared_relu", Params{{"hidden_size", width}, {"ff", f}}, prefix + ".mlp", true};
+            } else if (kind.string == "moe") {
+                const json::Value& router = C::need(mlp, "router", wm);
+                const json::Value& expert = C::need(mlp, "expert", wm);
+                const long long experts = C::integer(router, "experts", wm + "router."), top = C::integer(router, "top", wm + "router.");
+                const long long f = C::integer(expert, "ff", wm + "expert.");
+                const double limit = C::number(expert, "limit", wm + "expert.");
+                if (experts <= 0 || top <= 0 || top > experts || f <= 0 || limit <= 0.0)
+                    throw ConfigError(wm + "needs router.experts >= router.top > 0, expert.ff > 0 and expert.limit > 0");
+                Params e{{"hidden_size", width}, {"experts", experts}, {"top", top}, {"ff", f}, {"scoring", "sigmoid"}, {"correction", 0}, {"activation", "clamped"},
+                         {"limit", limit}, {"weight_input", 1}, {"shared_gated", 0}};
+                if (C::present(mlp, "shared")) {
+                    const json::Value& shared = *mlp.find("shared");
+                    const long long sf = C::integer(shared, "ff", wm + "shared.");
+                    const double sl = C::number(shared, "limit", wm + "shared.");
+                    if (sf <= 0 || sl <= 0.0) throw ConfigError(wm + "shared.ff and shared.limit must be > 0");
+                    e.set("shared_ff", sf);
+                    e.set("shared_activation", "clamped");
+                    e.set("shared_limit", sl);
+                }
+                ff = PartSpec{"routed_experts", e, prefix + ".mlp", true};
+            } else {
+                throw ConfigError(wm + "kind '" + kind.string + "' is no feed-forward of this design (dense, moe)");
+            }
+            // no norm of its own: it reads the rows of the mixer's norm, as they are in front of the convolution
+            layer.sublayers.push_back({"feed_forward", ff, PartSpec::none(), "pre", gain(prefix + ".ls2")});
+        } else {
+            spec.ignored_tensors.push_back(prefix + ".ls2");        // a layer without a feed-forward may still carry its gain
+        }
+        if (side > 0) {
+            PartSpec part{"token_side", Params{{"hidden_size", width}, {"vocab_size", vocab}, {"side", side}, {"column", (long long)i * side}, {"columns", count * side},
+                                               {"table", "side.embed"}}, prefix + ".side", true};
+            layer.sublayers.push_back({"feed_forward", part, PartSpec::none(), "pre",
+                                       PartSpec{"rmsnorm", Params{{"size", width}, {"eps", eps}, {"weight_name", ""}}, prefix + ".side.norm", true}});
+            layer.sequential_tail = 1;
+        }
+        spec.layers.push_back(std::move(layer));
+    }
+    for (int i = 0; i < (int)spec.layers.size(); ++i) spec.run_order.push_back(RunEntry{i, i, true});
+    spec.embedding = PartSpec{"embedding", Params{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}}, "embed", true};
+    spec.final_norm = single_norm("final.norm");
+    spec.lm_head = PartSpec{"lm_head", Params{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}}, "head", true};
+    return spec;
+}
+
 inline void register_builtin_architectures() {
     ArchitectureRegistry& r = ArchitectureRegistry::instance();
     for (auto& e : r.entries)
@@ -437,6 +557,7 @@ inline void register_builtin_architectures() {
     r.add("qwen2", qwen2_spec);
     r.add("gufanex", gufanex_spec);
     r.add("lasizen", lasizen_spec);
+    r.add("masezen", masezen_spec);
 }
 
 }  // namespace easygpt::engine

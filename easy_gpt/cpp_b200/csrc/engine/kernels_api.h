@@ -9,80 +9,44 @@ extern "C" {
 // activation.cu
 int eg_swiglu(cudaStream_t stream, int dtype, const void* gate_up, int ld, void* out, int ldo, int tokens, int inter);
 // attention_generic.cu
-int eg_attention_generic(cudaStream_t stream, int dtype, const void* q, int ldq, const void* k_cache,
-    const void* v_cache, const int* block_table, int table_stride, const int* token_seq, const int* positions,
-    void* out, int ldo, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size,
-    long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status);
+int eg_attention_generic(cudaStream_t stream, int dtype, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, void* out, int ldo, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status);
 // attention_paged.cu
-int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
-    const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* seq_context,
-    void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads, int num_kv_heads,
-    int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale,
-    int splits, int* status, const void* prefetch, long long prefetch_bytes, int* counters, int use_pdl,
-    unsigned long long* trace, const int* token_list);
+int eg_attention_paged(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int splits, int* status, const void* prefetch, long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list);
 // attention_paged.cu
-int eg_attention_prefill(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache,
-    const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out,
-    int ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride,
-    long long head_stride, int num_pages, int window, float scale, int* status);
+int eg_attention_prefill(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status);
 // attention_tcgen05.cu
-int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens,
-    const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions,
-    const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim,
-    int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status,
-    long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue);
+int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue);
 int eg_attention_prefill_groups(int head_dim);
 // embedding.cu
-int eg_embedding_gather(cudaStream_t stream, int dtype, const int* ids, const void* table, float* residual, int tokens,
-    int hidden, int vocab, int* status);
+int eg_embedding_gather(cudaStream_t stream, int dtype, const int* ids, const void* table, float* residual, int tokens, int hidden, int vocab, int* status);
 // engine_ops.cu
 int eg_add_into_f32(cudaStream_t stream, float* residual, const void* delta, int delta_dtype, long long n);
 // engine_ops.cu
 int eg_convert_rows(cudaStream_t stream, const void* src, int src_dtype, void* dst, int dst_dtype, long long n);
 // gemm_f32.cu
-int eg_gemm_f32_nt(cudaStream_t stream, const float* A, int lda, const float* W, int ldw, const float* bias, float* C,
-    int ldc, int M, int N, int K);
+int eg_gemm_f32_nt(cudaStream_t stream, const float* A, int lda, const float* W, int ldw, const float* bias, float* C, int ldc, int M, int N, int K);
 // gemm_skinny.cu
-int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw,
-    const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in, float* resid_out,
-    const void* delta, const float* gain, float eps, void* out, long long ldo, int row_blocks, int k_slices,
-    int k_split, float* scratch, int* counters, int num_heads, int num_kv_heads, int head_dim, const int* positions,
-    const int* slot_map, void* k_cache, void* v_cache, const float* inv_freq, int page_size, long long page_stride,
-    long long head_stride, long long pool_slots, int* status, const void* prefetch, long long prefetch_bytes,
-    unsigned long long* trace, const float* ss_in, int ss_parts, float* resid_inout, const float* gain_out,
-    void* xn_out, float* ss_out);
+int eg_gemm_skinny(cudaStream_t stream, int epilogue, int norm, int use_pdl, const void* W, long long ldw, const float* bias, int M, int N, int K, const void* x, long long ldx, const float* resid_in, float* resid_out, const void* delta, const float* gain, float eps, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int num_heads, int num_kv_heads, int head_dim, const int* positions, const int* slot_map, void* k_cache, void* v_cache, const float* inv_freq, int page_size, long long page_stride, long long head_stride, long long pool_slots, int* status, const void* prefetch, long long prefetch_bytes, unsigned long long* trace, const float* ss_in, int ss_parts, float* resid_inout, const float* gain_out, void* xn_out, float* ss_out);
 // gemm_tcgen05.cu
-int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
-    const float* bias, void* out, long long ldo, int M, int N, int K, int* status);
+int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out, long long ldo, int M, int N, int K, int* status);
 // gemm_tcgen05.cu
-int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
-    const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status, long long* trace);
+int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status, long long* trace);
 // norm.cu
-int eg_add_rmsnorm(cudaStream_t stream, int delta_dtype, int out_dtype, float* residual, const void* delta,
-    const int* rows, const float* gain, void* out, int num_rows, int hidden, float eps);
+int eg_add_rmsnorm(cudaStream_t stream, int delta_dtype, int out_dtype, float* residual, const void* delta, const int* rows, const float* gain, void* out, int num_rows, int hidden, float eps);
 // rope_cache.cu
-int eg_rope_table(cudaStream_t stream, const int* positions, const float* inv_freq, float* table, int tokens,
-    int half);
+int eg_rope_table(cudaStream_t stream, const int* positions, const float* inv_freq, float* table, int tokens, int half);
 // rope_cache.cu
-int eg_rope_cache_vec(cudaStream_t stream, int dtype, void* qkv, int ld, const float* table, const int* slot_map,
-    void* k_cache, void* v_cache, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size,
-    long long page_stride, long long head_stride, long long pool_slots, int* status);
+int eg_rope_cache_vec(cudaStream_t stream, int dtype, void* qkv, int ld, const float* table, const int* slot_map, void* k_cache, void* v_cache, int tokens, int num_heads, int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride, long long pool_slots, int* status);
 // rope_cache.cu
-int eg_rope_cache(cudaStream_t stream, int dtype, void* qkv, int ld, const float* bias, const int* positions,
-    const int* slot_map, void* k_cache, void* v_cache, const float* inv_freq, int tokens, int num_heads,
-    int num_kv_heads, int head_dim, int rotary_dim, int page_size, long long page_stride, long long head_stride,
-    long long pool_slots, int* status);
+int eg_rope_cache(cudaStream_t stream, int dtype, void* qkv, int ld, const float* bias, const int* positions, const int* slot_map, void* k_cache, void* v_cache, const float* inv_freq, int tokens, int num_heads, int num_kv_heads, int head_dim, int rotary_dim, int page_size, long long page_stride, long long head_stride, long long pool_slots, int* status);
 // sampling.cu
-int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, int* out,
-    int blocks_per_row, float* part_val, int* part_idx, int* counters);
+int eg_argmax(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, int* out, int blocks_per_row, float* part_val, int* part_idx, int* counters);
 // sampling.cu
-int eg_sample(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, const float* temperature,
-    const int* top_k, const float* top_p, const float* uniform, int* out);
+int eg_sample(cudaStream_t stream, const float* logits, long long ld, int rows, int vocab, const float* temperature, const int* top_k, const float* top_p, const float* uniform, int* out);
 // decode_fused.cu
 int eg_decode_fused_smem(int stages, int xs_bytes, int num_ops, int num_tmpls);
 // decode_fused.cu
-int eg_decode_fused(cudaStream_t stream, const void* tmpls, int num_tmpls, const void* ops, int num_ops, int tokens, int stages, int xs_bytes, int ctas,
-    unsigned* sync, int* status, unsigned long long* trace);
+int eg_decode_fused(cudaStream_t stream, const void* tmpls, int num_tmpls, const void* ops, int num_ops, int tokens, int stages, int xs_bytes, int ctas, unsigned* sync, int* status, unsigned long long* trace);
 // layernorm.cu
 int eg_add_layernorm(cudaStream_t stream, float* residual, const void* delta_a, int dtype_a, const void* delta_b, int dtype_b, const int* rows, const float* gain1, const float* bias1, void* out1, const float* gain2, const float* bias2, void* out2, int out_dtype, int num_rows, int hidden, float eps);
 // engine_ops.cu
@@ -106,13 +70,13 @@ int eg_attention_latent(cudaStream_t stream, int cache_dtype, const float* qa, c
 // attention_latent.cu
 int eg_latent_expand(cudaStream_t stream, int w_dtype, const float* o, const void* Uv, void* out, int out_dtype, long long ldo, int tokens, int heads, int vdim, int rank);
 // moe.cu
-int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w, float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top);
+int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w, float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top, int scoring);
 // moe.cu
-int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens, int width, int ff, int top, int experts);
+int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, const float* input_weights, void* act, int tokens, int width, int ff, int top, int experts, int activation, float limit);
 // moe.cu
 int eg_moe_combine(cudaStream_t stream, int dtype, const void* h, long long ld, const void* act, const void* down, const int* ids, const float* weights, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int ff, int top, int experts);
 // moe.cu
-int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, int* counts, int* starts, int* cursors, int* tile_group, int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows);
+int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, const float* input_weights, int* counts, int* starts, int* cursors, int* tile_group, int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows);
 // moe.cu
 int eg_moe_gather(cudaStream_t stream, const void* y, const int* row_of, const int* ids, const float* weights, const void* h, long long ld, const void* shared, int shared_dtype, const float* gate, float* out, int tokens, int width, int top, int experts);
 // gemm_tcgen05.cu
@@ -157,4 +121,34 @@ int eg_gemm_skinny_xielu(cudaStream_t stream, int use_pdl, const void* W, long l
 int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu
 int eg_gated_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* aux, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
+// conv_shift.cu
+int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, const float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out, int out_dtype, int tokens, int hidden, int taps);
+// conv_shift.cu
+int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, const float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps);
+// conv_shift.cu
+int eg_conv_shift_state(cudaStream_t stream, const float* rows, const float* gain, float eps, float* state, long long slot_floats, const int* seq_starts, const int* seq_slots, int num_seqs, int hidden, int taps);
+// attention_mixed.cu
+int eg_mixed_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* q_weight, const float* k_weight, float eps, const float* table, int rot_dims, float magnitude, const float* mix, float scale, const int* slot_map, void* k_cache, void* v_cache, long long head_stride, int page_size, long long page_stride, long long pool_slots, void* q_out, int q_dtype, int tokens, int heads, int kv_heads, int dk, int* status);
+// attention_mixed.cu
+int eg_mixed_attention(cudaStream_t stream, int dtype, const void* q, int q_dtype, const void* k_cache, const void* v_cache, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const float* gate, long long ld_gate, void* out, long long ldo, int num_tokens, int heads, int kv_heads, int dk, int page_size, long long page_stride, int num_pages, int* status);
+// token_side.cu
+int eg_token_side(cudaStream_t stream, int dtype, float* residual, const void* delta_a, int dtype_a, const float* scale_a, const void* delta_b, int dtype_b, const float* scale_b, const int* token_ids, const void* table, int vocab, const void* gate_w, const void* proj_w, const float* norm_gain, float eps, int tokens, int hidden, int side, int* status);
+// token_side.cu
+int eg_token_side_rows(cudaStream_t stream, int dtype, const void* rows, long long ld, float* y, const int* token_ids, const void* table, int vocab, const void* gate_w, const void* proj_w, int tokens, int hidden, int side, int* status);
+// token_side.cu
+int eg_add_scaled(cudaStream_t stream, float* residual, const void* delta, int delta_dtype, const float* scale, int tokens, int hidden);
+// activation.cu
+int eg_squared_relu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n);
+// activation.cu
+int eg_clamped_glu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float limit);
+// gemm_skinny.cu
+int eg_gemm_skinny_relu2(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status);
+// gemm_skinny.cu
+int eg_gemm_skinny_clamped_glu(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status, float limit);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_pair_relu2(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K, int tile_n, int* status);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_pair_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K, int* status, float limit);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_grouped_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status, float limit);
 }  // extern "C"

@@ -8,6 +8,7 @@
 #include "architectures.hpp"
 #include "parts.hpp"
 #include "parts_delta.hpp"
+#include "parts_mixed.hpp"
 #include "parts_sequence.hpp"
 
 namespace easygpt::engine {
@@ -37,7 +38,7 @@ struct SubLayer {
 // feed-forward) run the same parts with the additions and norms as kernels of their own.
 class Block {
 public:
-    explicit Block(const LayerSpec& spec) : parallel(spec.parallel) {
+    explicit Block(const LayerSpec& spec) : parallel(spec.parallel), tail(spec.sequential_tail) {
         PartRegistry& reg = PartRegistry::instance();
         if (spec.position.present) position = PartRegistry::find(reg.positions, "position", spec.position.kind)(spec.position.params, spec.position.prefix);
         auto make_norm = [&](const PartSpec& p) -> std::shared_ptr<Norm> {
@@ -94,33 +95,55 @@ public:
         }
     }
 
-    // x = x + (f1(norm1(x)) + f2(norm2(x)) + ...): every sub-layer reads the stream as it entered the layer.  The adds that
-    // the layer in front left and the first two norms are one kernel where the norms can pair up; the outputs of the
-    // first two sub-layers are handed on unadded, for the next norm to take in.
+    // x = x + (f1(norm1(x)) + f2(norm2(x)) + ...): every sub-layer of the group reads the stream as it entered the layer.  The
+    // adds that the layer in front left and the first two norms are one kernel where the norms can pair up; the outputs of
+    // the first two sub-layers are handed on unadded, for the next norm to take in.  A second sub-layer without a norm reads
+    // the first one's normed rows; a shift in front of the first sub-layer's part changes what that part reads only (norm and
+    // shift are one kernel with two outputs where the shift offers that).  An output "norm" of a group's sub-layer is a gain
+    // per channel that goes along with the output (Delta::scale).
     Stream forward_parallel(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, void* work2) const {
         const int T = ctx.num_tokens;
         const long long n = (long long)T * width_;
         if (s.delta.has_pre()) throw DeviceError("prepared rows reached a parallel layer");
+        const size_t group = sublayers.size() - (size_t)tail;
         std::vector<Delta> outputs;
-        for (size_t i = 0; i < sublayers.size(); ++i) {
+        for (size_t i = 0; i < group; ++i) {
             const SubLayer& sub = sublayers[i];
             void* rows = (i & 1) ? work2 : work;
             if (i == 0) {
-                const bool paired = sublayers.size() >= 2 &&
-                                    sub.norm->forward_pair(ctx, s.residual, s.delta.p, s.delta.dtype, s.delta2.p, s.delta2.dtype, sublayers[1].norm.get(), work, work2,
-                                                           ctx.dtype, T);
-                if (!paired) {
-                    settle(ctx, s, n, false);
-                    sub.norm->forward(ctx, s.residual, s.delta.p, s.delta.dtype, work, ctx.dtype, T, nullptr);
-                    if (sublayers.size() >= 2) sublayers[1].norm->forward(ctx, s.residual, nullptr, ctx.dtype, work2, ctx.dtype, T, nullptr);
+                const bool shares = group >= 2 && !sublayers[1].norm;          // the second sub-layer reads this norm's rows
+                if (sub.shift) {
+                    if (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()) throw DeviceError("a shift was handed no state of its size");
+                    settle(ctx, s, n, true);
+                    const float* gain = nullptr;
+                    float eps = 0.f;
+                    if (!(sub.norm->rms_parameters(&gain, &eps) &&
+                          sub.shift->forward_rms(ctx, s.residual, gain, eps, cache.layer_state, cache.layer_state_floats, work, shares ? work2 : nullptr, ctx.dtype))) {
+                        float* normed = s.spare;                 // free between layers
+                        sub.norm->forward(ctx, s.residual, nullptr, DType::F32, normed, DType::F32, T, nullptr);
+                        sub.shift->forward(ctx, normed, cache.layer_state, cache.layer_state_floats, work, ctx.dtype);
+                        if (shares) launch_check(eg_convert_rows(ctx.stream, normed, (int)DType::F32, work2, (int)ctx.dtype, n), "convert");
+                    }
+                    if (group >= 2 && !shares) sublayers[1].norm->forward(ctx, s.residual, nullptr, ctx.dtype, work2, ctx.dtype, T, nullptr);
+                } else {
+                    const bool paired = group >= 2 && !shares &&
+                                        sub.norm->forward_pair(ctx, s.residual, s.delta.p, s.delta.dtype, s.delta2.p, s.delta2.dtype, sublayers[1].norm.get(), work, work2,
+                                                               ctx.dtype, T);
+                    if (!paired) {
+                        settle(ctx, s, n, false);
+                        sub.norm->forward(ctx, s.residual, s.delta.p, s.delta.dtype, work, ctx.dtype, T, nullptr);
+                        if (!shares && group >= 2) sublayers[1].norm->forward(ctx, s.residual, nullptr, ctx.dtype, work2, ctx.dtype, T, nullptr);
+                    }
                 }
                 s.delta = s.delta2 = Delta();
             } else if (i >= 2) {
                 sub.norm->forward(ctx, s.residual, nullptr, ctx.dtype, rows, ctx.dtype, T, nullptr);
             }
+            if (i == 1 && !sub.norm && !sublayers[0].shift) rows = work;       // the first norm's rows, unshifted: the same buffer
             if (i >= 2) {
                 // the arena about to be reused holds the output of the sub-layer before the last: it goes into the spare buffer
                 Delta& old = outputs[i - 2];
+                if (old.scale) throw DeviceError("a parallel layer with output gains has at most two sub-layers in its group");
                 if (i == 2) launch_check(eg_convert_rows(ctx.stream, old.p, (int)old.dtype, s.spare, (int)DType::F32, n), "convert");
                 else launch_check(eg_add_into_f32(ctx.stream, s.spare, old.p, (int)old.dtype, n), "add");
                 old = Delta();
@@ -131,6 +154,10 @@ public:
             in.rows = Rows{rows, ctx.dtype, T, width_, width_};
             Delta d = sub.mixer ? sub.mixer->forward(ctx, in, cache, nullptr) : sub.feed_forward->forward(ctx, in, nullptr);
             if (d.has_pre()) throw DeviceError("a part returned prepared rows without having been offered the norm that follows");
+            if (sub.output_norm) {
+                d.scale = sub.output_norm->plain_gain();
+                if (!d.scale) throw DeviceError("a parallel sub-layer's output norm must be a plain gain per channel");
+            }
             outputs.push_back(d);
         }
         const size_t k = outputs.size();
@@ -140,7 +167,38 @@ public:
         }
         s.delta = outputs[k - 1];
         if (k >= 2) s.delta2 = outputs[k - 2];
+        // the sub-layers behind the group, one after the other; the first may take the group's outputs into its own kernel
+        for (size_t i = group; i < sublayers.size(); ++i) {
+            const SubLayer& sub = sublayers[i];
+            const float* gain = nullptr;
+            float eps = 0.f;
+            if (sub.feed_forward && !sub.norm && sub.output_norm && sub.output_norm->rms_parameters(&gain, &eps) &&
+                sub.feed_forward->forward_joined(ctx, s.residual, s.delta, s.delta2, gain, eps)) {
+                s.delta = s.delta2 = Delta();
+                continue;
+            }
+            settle_scaled(ctx, s, T);
+            if (sub.norm || !sub.feed_forward || !sub.output_norm) throw DeviceError("a sub-layer behind a parallel group reads the stream itself and joins it through a norm");
+            launch_check(eg_convert_rows(ctx.stream, s.residual, (int)DType::F32, work, (int)ctx.dtype, n), "convert");
+            ctx.arena = &arenas.sub[(*turn)++ & 1];
+            ctx.arena->reset();
+            PartInput in;
+            in.rows = Rows{work, ctx.dtype, T, width_, width_};
+            Delta d = sub.feed_forward->forward(ctx, in, nullptr);
+            if (!sub.output_norm->add_normed(ctx, s.residual, d.p, d.dtype, T)) throw DeviceError("the output norm of a sub-layer behind a parallel group cannot join the stream");
+        }
+        // a gain never leaves the layer: what is still pending with one is added here
+        if (s.delta.scale || s.delta2.scale) settle_scaled(ctx, s, T);
         return s;
+    }
+    // adds what is pending, each with its gain if it has one
+    void settle_scaled(const StepContext& ctx, Stream& s, int T) const {
+        for (Delta* d : {&s.delta2, &s.delta}) {
+            if (!d->has_delta()) continue;
+            if (d->scale) launch_check(eg_add_scaled(ctx.stream, s.residual, d->p, (int)d->dtype, d->scale, T, width_), "add_scaled");
+            else launch_check(eg_add_into_f32(ctx.stream, s.residual, d->p, (int)d->dtype, (long long)T * width_), "add");
+            *d = Delta();
+        }
     }
 
     // Returns the buffer that now holds the residual stream, the other one, and what the last sub-layer left still to be
@@ -195,7 +253,7 @@ public:
                 const float* gain = nullptr;
                 float eps = 0.f;
                 if (!(sub.norm->rms_parameters(&gain, &eps) &&
-                      sub.shift->forward_rms(ctx, s.residual, gain, eps, cache.layer_state, cache.layer_state_floats, work, ctx.dtype))) {
+                      sub.shift->forward_rms(ctx, s.residual, gain, eps, cache.layer_state, cache.layer_state_floats, work, nullptr, ctx.dtype))) {
                     float* normed = ctx.take<float>((size_t)n);
                     sub.norm->forward(ctx, s.residual, nullptr, DType::F32, normed, DType::F32, T, nullptr);
                     sub.shift->forward(ctx, normed, cache.layer_state, cache.layer_state_floats, work, ctx.dtype);
@@ -245,6 +303,7 @@ public:
     std::shared_ptr<PositionEncoding> position;
     Mixer* mixer = nullptr;
     bool parallel = false;
+    int tail = 0;                       // with parallel: the last `tail` sub-layers follow the group one after the other
     int width_ = 0;                     // the model's width (for sub-layers without a norm of their own)
 };
 
@@ -262,6 +321,7 @@ public:
         register_builtin_parts();
         register_sequence_parts();
         register_delta_parts();
+        register_mixed_parts();
         spec.validate();
         PartRegistry& reg = PartRegistry::instance();
         embedding = PartRegistry::find(reg.embeddings, "embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding.prefix);
@@ -317,6 +377,7 @@ public:
         for (auto& b : blocks)                                   // a layer's position encoding may have tensors of its own
             if (b->position)
                 for (auto& r : b->position->tensor_requests()) out.push_back(r);
+        for (auto& name : spec.ignored_tensors) out.push_back(TensorRequest::ignored(name));
         return out;
     }
     void load_weights(const std::string& model_file) {

@@ -152,6 +152,34 @@ public:
         return out;
     }
 
+    // the same with act(z) = max(z, 0)^2 (limit 0), or, over interleaved gate and up rows, the clamped gate (limit > 0):
+    // out [M, out_features / 2]
+    Rows skinny_relu2(const StepContext& ctx, const Rows& x) const { return skinny_act(ctx, x, 0.f); }
+    Rows skinny_clamped_glu(const StepContext& ctx, const Rows& x, float limit) const { return skinny_act(ctx, x, limit); }
+    Rows skinny_act(const StepContext& ctx, const Rows& x, float limit) const {
+        const int M = x.rows, N = out_features;
+        const plans::SkinnyPlan plan = plans::skinny_plan(N, in_features, 0);
+        float* partials = nullptr;
+        int* counters = nullptr;
+        if (plan.k_split > 1) {
+            const size_t groups = (size_t)(N + plan.row_blocks * 16 - 1) / (plan.row_blocks * 16);
+            const size_t floats = (size_t)plan.k_split * groups * plan.row_blocks * 16 * plans::skinny_padded_tokens(M);
+            if (floats > KernelScratch::SKINNY_FLOATS || groups > KernelScratch::SKINNY_COUNTERS)
+                throw DeviceError("a decode product's split needs more scratch memory than the engine holds");
+            partials = ctx.scratch->skinny_partials.as<float>();
+            counters = ctx.scratch->skinny_counters.as<int>();
+        }
+        const int cols = limit > 0.f ? N / 2 : N;
+        Rows out{ctx.take_rows(M, cols, DType::BF16), DType::BF16, M, cols, cols};
+        if (limit > 0.f)
+            launch_check(eg_gemm_skinny_clamped_glu(ctx.stream, plans::use_pdl(), weight, in_features, M, N, in_features, x.p, x.ld, out.p, cols, plan.row_blocks,
+                                                    plan.k_slices, plan.k_split, partials, counters, ctx.status, limit), "gemm_skinny_clamped_glu");
+        else
+            launch_check(eg_gemm_skinny_relu2(ctx.stream, plans::use_pdl(), weight, in_features, M, N, in_features, x.p, x.ld, out.p, N, plan.row_blocks,
+                                              plan.k_slices, plan.k_split, partials, counters, ctx.status), "gemm_skinny_relu2");
+        return out;
+    }
+
     // whether with_following_norm can run for this input (the decode kernel takes it)
     bool takes_following_norm(const Rows& x) const {
         return dtype == DType::BF16 && plans::gemm_skinny_takes(dtype, x.rows, in_features) && x.rows <= plans::FUSED_NORM_MAX_TOKENS && aligned(x);
@@ -205,14 +233,18 @@ private:
 };
 
 // ---- RMSNorm: y = w * (x / sqrt(mean(x^2) + eps)) (src/models/norm.cpp:46-60), eps a parameter (the reference fixes
-// 1e-6, src/models/norm.cpp:41), fused with the float32 residual add ---------------------------------------------------
+// 1e-6, src/models/norm.cpp:41), fused with the float32 residual add; with single_gain the stored gain is one number ---------------------------------------------------
 class RMSNorm : public Norm {
 public:
     RMSNorm(const Params& p, const std::string& prefix)
-        : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")) {}
-    std::vector<TensorRequest> tensor_requests() const override { return {TensorRequest::vector(weight_name_, size_).with_init("one")}; }
+        : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")),
+          single_(p.integer("single_gain", 0) != 0) {}
+    std::vector<TensorRequest> tensor_requests() const override {
+        return {(single_ ? TensorRequest::scalar(weight_name_) : TensorRequest::vector(weight_name_, size_)).with_init("one")};
+    }
     void load(const HostTensors& file, DType) override {
-        const std::vector<float> g = host_floats(need_tensor(file, weight_name_));       // gains are used in float32 whatever they were stored in
+        std::vector<float> g = host_floats(need_tensor(file, weight_name_));       // gains are used in float32 whatever they were stored in
+        if (single_) g.assign((size_t)size_, g.at(0));                               // one number for all coordinates: the kernels read a gain per channel
         gain_ = upload(g.data(), g.size(), DType::F32);
     }
     size_t weight_bytes() const override { return (size_t)size_ * 4; }
@@ -247,6 +279,7 @@ private:
     int size_;
     float eps_;
     std::string weight_name_;      // parameter weight_name: the gain's tensor name as a suffix of the prefix (default ".weight")
+    bool single_;                  // parameter single_gain: the tensor is ONE number, the gain of every coordinate
     DeviceBuffer gain_;
 };
 
@@ -640,7 +673,11 @@ public:
     SwiGLU(const Params& p, const std::string& prefix)
         : FeedForward(p, prefix), hidden_((int)p.integer("hidden_size")), inter_((int)p.integer("intermediate_size")), bias_(p.flag("bias", false)),
           gate_name_(prefix + p.text("gate_name", ".gate_proj.weight")), up_name_(prefix + p.text("up_name", ".up_proj.weight")),
-          down_name_(prefix + p.text("down_name", ".down_proj.weight")) {}
+          down_name_(prefix + p.text("down_name", ".down_proj.weight")), clamped_(p.text("activation", "swiglu") == "clamped"),
+          limit_((float)p.real("limit", 0.0)) {
+        if (p.text("activation", "swiglu") != "swiglu" && !clamped_) throw std::invalid_argument("a gated feed-forward's activation is 'swiglu' or 'clamped'");
+        if (clamped_ && !(limit_ > 0.f)) throw std::invalid_argument("a clamped gate needs a positive limit");
+    }
     std::vector<TensorRequest> tensor_requests() const override {
         std::vector<TensorRequest> r = {TensorRequest::matrix(gate_name_, inter_, hidden_), TensorRequest::matrix(up_name_, inter_, hidden_),
                                         TensorRequest::matrix(down_name_, hidden_, inter_)};
@@ -670,12 +707,12 @@ public:
     }
     size_t weight_bytes() const override { return gate_up_.weight_bytes() + down_.weight_bytes(); }
     bool capturable() const override { return true; }
-    bool accepts_pending_norm() const override { return true; }
-    bool fuses_following_norm() const override { return true; }
+    bool accepts_pending_norm() const override { return !clamped_; }
+    bool fuses_following_norm() const override { return !clamped_; }
 
     // norm + gate/up + SwiGLU; down projection into the residual
     bool emit_fused(FusedBuilder& b, const float* gain, float eps) const override {
-        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || inter_ % 8) return false;
+        if (b.ctx->dtype != DType::BF16 || hidden_ != b.hidden || inter_ % 8 || clamped_) return false;
         void* act = b.arena->take((size_t)b.tokens * inter_ * 2);
         EgFusedTemplate t = FusedBuilder::blank();
         t.input = EGF_IN_NORM;
@@ -707,6 +744,24 @@ public:
         const int T = ctx.num_tokens;
         const DType dtype = ctx.dtype;
         Rows act{ctx.take_rows(T, inter_, dtype), dtype, T, inter_, inter_};
+        if (clamped_) {
+            // g = min(gate, limit), u = clamp(up, -limit, limit): a = g sigmoid(1.702 g) (u + 1)
+            const Rows x = in.pending ? in.pending->materialize() : in.rows;
+            if (plans::gemm_skinny_takes(dtype, T, hidden_) && Linear::aligned(x)) {
+                act = gate_up_.skinny_clamped_glu(ctx, x, limit_);
+            } else if (plans::gemm_tcgen05_wide_takes(dtype, T, 2 * inter_, hidden_) && Linear::aligned(x)) {
+                launch_check(eg_gemm_tcgen05_pair_glu(ctx.stream, x.p, x.ld, gate_up_.weight, hidden_, act.p, inter_, T, 2 * inter_, hidden_, ctx.status, limit_),
+                             "gemm_tcgen05_pair_glu");
+            } else {
+                const Rows gu = gate_up_(ctx, x, /*out_f32=*/true);
+                launch_check(eg_clamped_glu(ctx.stream, gu.p, (int)gu.dtype, gu.ld, act.p, (int)dtype, inter_, T, inter_, limit_), "clamped_glu");
+            }
+            const Rows o = down_(ctx, act, /*out_f32=*/true);
+            Delta d;
+            d.p = o.p;
+            d.dtype = o.dtype;
+            return d;
+        }
         if (in.pending && in.pending->fusable) {
             // decode: add + norm + gate/up product + SwiGLU in one kernel
             const NormInFront norm = in.pending->fused();
@@ -739,6 +794,8 @@ private:
     int hidden_, inter_;
     bool bias_;
     std::string gate_name_, up_name_, down_name_;      // the weights' tensor names (parameters gate_name / up_name / down_name: suffixes of the prefix)
+    bool clamped_;                                     // parameter activation "clamped" (with limit) instead of "swiglu"
+    float limit_;
     Linear gate_up_, down_;
 };
 

@@ -210,20 +210,24 @@ public:
                                  void* /*out*/, DType /*out_dtype*/) const {
         return false;
     }
+    // the gain [size] (float32, device) if this part only multiplies every channel by a number of its own (no
+    // normalisation: a layer scale on a branch's output); a branch's output can then carry the gain along to the add
+    virtual const float* plain_gain() const { return nullptr; }
     virtual int size() const = 0;
 };
 
-// A mix of every token's row with the row of the token in front of it in its request, between a norm and the part that
-// reads it.  Per request it keeps `state_floats()` float32 values (the last row of earlier steps; zeros at the start).
+// A mix of every token's row with the rows of the tokens in front of it in its request, between a norm and the part that
+// reads it.  Per request it keeps `state_floats()` float32 values (the last rows of earlier steps; zeros at the start).
 class Shift : public Part {
 public:
     using Part::Part;
     virtual long long state_floats() const = 0;
     // rows float32 [T, size] (normed) -> out [T, size] in out_dtype; state [slots, slot_floats], this part's values first
     virtual void forward(const StepContext& ctx, const float* rows, float* state, long long slot_floats, void* out, DType out_dtype) const = 0;
-    // the same with the norm in front (a plain RMSNorm: gain, eps) done here from the float32 stream; false: cannot
+    // the same with the norm in front (a plain RMSNorm: gain, eps) done here from the float32 stream; with plain_out also the
+    // normed rows as they are (for a part beside the mixer that reads the same norm); false: cannot
     virtual bool forward_rms(const StepContext& /*ctx*/, const float* /*residual*/, const float* /*gain*/, float /*eps*/, float* /*state*/,
-                             long long /*slot_floats*/, void* /*out*/, DType /*out_dtype*/) const {
+                             long long /*slot_floats*/, void* /*out*/, void* /*plain_out*/, DType /*out_dtype*/) const {
         return false;
     }
 };
@@ -249,6 +253,7 @@ struct PreNormed {
 struct Delta {
     void* p = nullptr;
     DType dtype = DType::BF16;
+    const float* scale = nullptr;       // a gain per channel (float32 [hidden]) that the add applies: x += scale * p
     PreNormed pre;
     bool has_delta() const { return p != nullptr; }
     bool has_pre() const { return pre.norm != nullptr; }
@@ -438,6 +443,12 @@ public:
     virtual bool accepts_pending_norm() const { return false; }
     virtual bool fuses_following_norm() const { return false; }
     virtual Delta forward(const StepContext& ctx, PartInput x, const FollowingNorm* follow) = 0;
+    // For a sub-layer that reads the stream itself (no norm in front) and joins it through an RMS norm on its output: the
+    // whole of  x += a + b (what is still to be added, each with its gain);  x += gain * y / rms(y), y = this(x)  in the part's
+    // own kernels.  false: the part cannot, and the block adds, converts, calls forward and norms step by step.
+    virtual bool forward_joined(const StepContext& /*ctx*/, float* /*residual*/, const Delta& /*a*/, const Delta& /*b*/, const float* /*gain*/, float /*eps*/) {
+        return false;
+    }
     virtual bool emit_fused(FusedBuilder&, const float* /*gain*/, float /*eps*/) const { return false; }
 };
 

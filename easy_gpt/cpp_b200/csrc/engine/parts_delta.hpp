@@ -31,7 +31,8 @@ public:
                                     ctx.num_tokens, size_), "token_shift");
     }
     bool forward_rms(const StepContext& ctx, const float* residual, const float* gain, float eps, float* state, long long slot_floats, void* out,
-                     DType out_dtype) const override {
+                     void* plain_out, DType out_dtype) const override {
+        if (plain_out) return false;        // the fused kernel leaves the mixed rows only
         launch_check(eg_rmsnorm_shift(ctx.stream, residual, gain, eps, mu_.as<float>(), state, slot_floats, ctx.token_seq, ctx.seq_starts, ctx.seq_slots, out,
                                       (int)out_dtype, ctx.num_tokens, size_), "rmsnorm_shift");
         return true;

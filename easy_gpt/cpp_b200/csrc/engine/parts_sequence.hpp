@@ -255,21 +255,36 @@ private:
 // Parameters: hidden_size, experts, identity, top, ff, shared_ff.  Tensors: .router [experts + identity, hidden],
 // .correction [experts + identity], .e<i>.gate / .up [ff, hidden], .e<i>.down [hidden, ff], .shared.gate / .up / .down,
 // .shared.sg [1, hidden].
+// Further parameters, each with the default that leaves the above as it is: scoring "sigmoid" (s = sigmoid(logits) instead of
+// the softmax); correction 0 (no .correction tensor); activation "clamped" with limit (an expert is
+// down(g sigmoid(1.702 g) (u + 1)), g = min(gate x, limit), u = clamp(up x, -limit, limit)); weight_input 1 (the weight
+// multiplies the expert's input, out = sum of expert(weight * h), not its output); shared_gated 0 (the shared expert is added
+// as it is, no .shared.sg), shared_activation / shared_limit (the shared expert's own form).
 class RoutedExperts : public FeedForward {
 public:
     RoutedExperts(const Params& p, const std::string& prefix)
         : FeedForward(p, prefix), hidden_((int)p.integer("hidden_size")), experts_((int)p.integer("experts")), identity_((int)p.integer("identity", 0)),
-          top_((int)p.integer("top")), ff_((int)p.integer("ff", 0)), shared_ff_((int)p.integer("shared_ff", 0)) {
+          top_((int)p.integer("top")), ff_((int)p.integer("ff", 0)), shared_ff_((int)p.integer("shared_ff", 0)),
+          sigmoid_(p.text("scoring", "softmax") == "sigmoid"), corrected_(p.integer("correction", 1) != 0), clamped_(p.text("activation", "swiglu") == "clamped"),
+          weight_input_(p.integer("weight_input", 0) != 0), shared_gated_(p.integer("shared_gated", 1) != 0), limit_((float)p.real("limit", 0.0)) {
+        if (p.text("scoring", "softmax") != "softmax" && !sigmoid_) throw std::invalid_argument("a routed feed-forward's scoring is 'softmax' or 'sigmoid'");
+        if (p.text("activation", "swiglu") != "swiglu" && !clamped_) throw std::invalid_argument("a routed feed-forward's activation is 'swiglu' or 'clamped'");
+        if (clamped_ && !(limit_ > 0.f)) throw std::invalid_argument("a clamped gate needs a positive limit");
+        if (weight_input_ && identity_ > 0) throw std::invalid_argument("identity outputs take their weight on the output");
         if (experts_ < 0 || identity_ < 0 || experts_ + identity_ <= 0) throw std::invalid_argument("a routed feed-forward needs at least one router output");
         if (top_ < 1 || top_ > experts_ + identity_) throw std::invalid_argument("a routed feed-forward chooses between 1 and all of its router outputs");
         if (experts_ > 0 && ff_ <= 0) throw std::invalid_argument("a routed feed-forward's experts need a positive ff");
         if (experts_ + identity_ > 2048) throw std::invalid_argument("a routed feed-forward takes at most 2048 router outputs");
-        if (shared_ff_ > 0)
-            shared_ = std::make_shared<SwiGLU>(Params{{"hidden_size", hidden_}, {"intermediate_size", shared_ff_}, {"gate_name", ".gate"}, {"up_name", ".up"}, {"down_name", ".down"}},
-                                               prefix + ".shared");
+        if (shared_ff_ > 0) {
+            Params sp{{"hidden_size", hidden_}, {"intermediate_size", shared_ff_}, {"gate_name", ".gate"}, {"up_name", ".up"}, {"down_name", ".down"}};
+            if (p.has("shared_activation")) sp.set("activation", p.text("shared_activation"));
+            if (p.has("shared_limit")) sp.set("limit", p.real("shared_limit"));
+            shared_ = std::make_shared<SwiGLU>(sp, prefix + ".shared");
+        }
     }
     std::vector<TensorRequest> tensor_requests() const override {
-        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".router", experts_ + identity_, hidden_), TensorRequest::vector(prefix + ".correction", experts_ + identity_).with_init("zero")};
+        std::vector<TensorRequest> r = {TensorRequest::matrix(prefix + ".router", experts_ + identity_, hidden_)};
+        if (corrected_) r.push_back(TensorRequest::vector(prefix + ".correction", experts_ + identity_).with_init("zero"));
         for (int e = 0; e < experts_; ++e) {
             const std::string ep = prefix + ".e" + std::to_string(e);
             r.push_back(TensorRequest::matrix(ep + ".gate", ff_, hidden_));
@@ -278,7 +293,7 @@ public:
         }
         if (shared_) {
             for (auto& t : shared_->tensor_requests()) r.push_back(t);
-            r.push_back(TensorRequest{prefix + ".shared.sg", {{1, hidden_}, {hidden_}}, false, ""});
+            if (shared_gated_) r.push_back(TensorRequest{prefix + ".shared.sg", {{1, hidden_}, {hidden_}}, false, ""});
         }
         return r;
     }
@@ -288,7 +303,7 @@ public:
             return upload(v.data(), v.size(), DType::F32);
         };
         router_ = f32(".router");
-        correction_ = f32(".correction");
+        if (corrected_) correction_ = f32(".correction");
         // all experts in one block each: gate and up rows interleaved per hidden unit (gate_f, up_f), and the down maps
         std::vector<float> gu((size_t)experts_ * 2 * ff_ * hidden_), dn((size_t)experts_ * hidden_ * ff_);
         for (int e = 0; e < experts_; ++e) {
@@ -307,7 +322,7 @@ public:
         dtype_ = dtype;
         if (shared_) {
             shared_->load(file, dtype);
-            shared_gate_ = f32(".shared.sg");
+            if (shared_gated_) shared_gate_ = f32(".shared.sg");
         }
     }
     // a step reads the router, and per token `top` experts at most (all of them once there are many tokens)
@@ -329,10 +344,15 @@ public:
         const Rows h = in.pending ? in.pending->materialize() : in.rows;
         int* ids = ctx.take<int>((size_t)T * top_);
         float* weights = ctx.take<float>((size_t)T * top_);
-        float* gate = shared_ ? ctx.take<float>((size_t)T) : nullptr;
+        const bool gated = shared_ && shared_gated_;
+        float* gate = gated ? ctx.take<float>((size_t)T) : nullptr;
         float* scores = ctx.take<float>((size_t)T * (experts_ + identity_));
-        launch_check(eg_moe_route(ctx.stream, (int)dtype, h.p, h.ld, router_.as<float>(), correction_.as<float>(), shared_ ? shared_gate_.as<float>() : nullptr,
-                                  scores, ids, weights, gate, T, hidden_, experts_ + identity_, top_), "moe_route");
+        launch_check(eg_moe_route(ctx.stream, (int)dtype, h.p, h.ld, router_.as<float>(), corrected_ ? correction_.as<float>() : nullptr,
+                                  gated ? shared_gate_.as<float>() : nullptr, scores, ids, weights, gate, T, hidden_, experts_ + identity_, top_, sigmoid_ ? 1 : 0),
+                     "moe_route");
+        // where the weight multiplies an expert's input, the sums over the chosen experts count every term once
+        const float* in_w = weight_input_ ? weights : nullptr;
+        const float* out_w = weight_input_ ? nullptr : weights;
         Delta shared;
         if (shared_) {
             PartInput rows;
@@ -347,14 +367,18 @@ public:
             int *counts = scratch, *starts = counts + experts_, *cursors = starts + experts_ + 1, *tile_group = cursors + experts_,
                 *row_of = tile_group + max_rows / 128;
             void* rows = ctx.take_rows(max_rows, hidden_, dtype);
-            launch_check(eg_moe_dispatch(ctx.stream, h.p, h.ld, ids, counts, starts, cursors, tile_group, row_of, rows, T, hidden_, top_, experts_, max_rows),
+            launch_check(eg_moe_dispatch(ctx.stream, h.p, h.ld, ids, in_w, counts, starts, cursors, tile_group, row_of, rows, T, hidden_, top_, experts_, max_rows),
                          "moe_dispatch");
             void* hidden = ctx.take_rows(max_rows, ff_, dtype);
-            launch_check(eg_gemm_tcgen05_grouped(ctx.stream, plans::EPI_SWIGLU, rows, hidden_, gate_up_.get(), hidden_, hidden, ff_, max_rows, 2 * ff_, hidden_,
-                                                 experts_, tile_group, ctx.status), "gemm_tcgen05_grouped");
+            if (clamped_)
+                launch_check(eg_gemm_tcgen05_grouped_glu(ctx.stream, rows, hidden_, gate_up_.get(), hidden_, hidden, ff_, max_rows, 2 * ff_, hidden_, experts_,
+                                                         tile_group, ctx.status, limit_), "gemm_tcgen05_grouped_glu");
+            else
+                launch_check(eg_gemm_tcgen05_grouped(ctx.stream, plans::EPI_SWIGLU, rows, hidden_, gate_up_.get(), hidden_, hidden, ff_, max_rows, 2 * ff_, hidden_,
+                                                     experts_, tile_group, ctx.status), "gemm_tcgen05_grouped");
             launch_check(eg_gemm_tcgen05_grouped(ctx.stream, plans::EPI_STORE, hidden, ff_, down_.get(), ff_, rows, hidden_, max_rows, hidden_, ff_, experts_,
                                                  tile_group, ctx.status), "gemm_tcgen05_grouped");
-            launch_check(eg_moe_gather(ctx.stream, rows, row_of, ids, weights, h.p, h.ld, shared.p, (int)shared.dtype, gate, out, T, hidden_, top_, experts_),
+            launch_check(eg_moe_gather(ctx.stream, rows, row_of, ids, out_w, h.p, h.ld, shared.p, (int)shared.dtype, gate, out, T, hidden_, top_, experts_),
                          "moe_gather");
             Delta d;
             d.p = out;
@@ -362,8 +386,9 @@ public:
             return d;
         }
         void* act = ctx.take_rows((size_t)T * top_, std::max(ff_, 1), dtype);
-        launch_check(eg_moe_hidden(ctx.stream, (int)dtype, h.p, h.ld, gate_up_.get(), ids, act, T, hidden_, ff_, top_, experts_), "moe_hidden");
-        launch_check(eg_moe_combine(ctx.stream, (int)dtype, h.p, h.ld, act, down_.get(), ids, weights, shared.p, (int)shared.dtype, gate, out, T, hidden_, ff_,
+        launch_check(eg_moe_hidden(ctx.stream, (int)dtype, h.p, h.ld, gate_up_.get(), ids, in_w, act, T, hidden_, ff_, top_, experts_, clamped_ ? 1 : 0, limit_),
+                     "moe_hidden");
+        launch_check(eg_moe_combine(ctx.stream, (int)dtype, h.p, h.ld, act, down_.get(), ids, out_w, shared.p, (int)shared.dtype, gate, out, T, hidden_, ff_,
                                     top_, experts_), "moe_combine");
         Delta d;
         d.p = out;
@@ -373,6 +398,8 @@ public:
 
 private:
     int hidden_, experts_, identity_, top_, ff_, shared_ff_;
+    bool sigmoid_, corrected_, clamped_, weight_input_, shared_gated_;
+    float limit_;
     DType dtype_ = DType::BF16;
     std::shared_ptr<SwiGLU> shared_;
     DeviceBuffer router_, correction_, gate_up_, down_, shared_gate_;

@@ -90,6 +90,7 @@ inline void write_random_model(const std::string& folder, const std::string& con
             if (gain || r.init == "one") v = 1.0f + (gain_std > 0 ? (float)(g.next() * gain_std) : 0.0f);
             else if (r.init == "zero") v = 0.0f;
             else if (r.init == "half") v = 0.5f;
+            else if (r.init == "identity") v = (i / (size_t)r.shapes[0].back() == i % (size_t)r.shapes[0].back() ? 1.0f : 0.0f) + (float)(g.next() * std_dev);
             else if (r.init == "log_decay") v = (float)std::log(1.0 + 15.0 * (0.5 + 0.5 * std::erf(g.next() / std::sqrt(2.0))));
             else if (r.init == "step_bias") v = (float)std::log(std::expm1(std::pow(10.0, -3.0 + 2.0 * (0.5 + 0.5 * std::erf(g.next() / std::sqrt(2.0))))));
             else v = (float)(g.next() * (vector ? bias_std : std_dev));

@@ -49,6 +49,7 @@ public:
         if (p.type != Param::Int && p.type != Param::Real) throw std::invalid_argument("parameter '" + key + "' must be a number");
         return p.r;
     }
+    double real(const std::string& key, double fallback) const { return has(key) ? real(key) : fallback; }
     bool flag(const std::string& key, bool fallback) const {
         if (!has(key)) return fallback;
         const Param& p = map_.at(key);
@@ -105,8 +106,14 @@ struct LayerSpec {
     std::vector<SubLayerSpec> sublayers;
     PartSpec position = PartSpec::none();     // handed to the layer's mixer
     // parallel: every sub-layer reads the stream as it entered the layer, x = x + (f1(norm1(x)) + f2(norm2(x)) + ...);
-    // each sub-layer then has a norm in front ("pre") and none behind
+    // each sub-layer then has a norm in front ("pre") and none behind.  The second sub-layer may have no norm of its own and
+    // then reads the rows of the first one's norm (x = x + f1(shift(n(x))) + f2(n(x)): a shift in front of the mixer changes
+    // what the mixer reads only).  An output_norm of a parallel sub-layer must be a plain gain per channel (a layer scale),
+    // which multiplies the branch's output before the sum.
     bool parallel = false;
+    // with parallel: the last `sequential_tail` sub-layers are not part of the parallel group but follow it one after the other,
+    // each on the stream as the one before left it (by the rules of a layer that is not parallel)
+    int sequential_tail = 0;
 
     // the common block x += mixer(norm1(x)); x += feed_forward(norm2(x))
     static LayerSpec pre_norm(PartSpec mixer, PartSpec feed_forward, PartSpec mixer_norm, PartSpec feed_forward_norm, PartSpec position) {
@@ -141,6 +148,7 @@ struct ModelSpec {
     PartSpec embedding_position = PartSpec::none();
     std::vector<PartSpec> stream_adds;
     long long bos_token_id = -1, eos_token_id = -1;
+    std::vector<std::string> ignored_tensors;     // names the file may hold although no part of this model reads them
 
     void validate() const {
         std::map<int, int> owner;
@@ -170,14 +178,19 @@ struct ModelSpec {
         for (auto& l : layers) {
             int mixers = 0;
             if (l.sublayers.empty()) throw std::invalid_argument("a layer needs at least one sub-layer");
-            for (auto& s : l.sublayers) {
+            if (l.sequential_tail < 0 || (l.sequential_tail > 0 && !l.parallel) || l.sequential_tail >= (int)l.sublayers.size())
+                throw std::invalid_argument("sequential_tail counts sub-layers behind a parallel group of at least one");
+            const size_t group = l.parallel ? l.sublayers.size() - (size_t)l.sequential_tail : 0;
+            for (size_t i = 0; i < l.sublayers.size(); ++i) {
+                const SubLayerSpec& s = l.sublayers[i];
                 if (s.role != "mixer" && s.role != "feed_forward") throw std::invalid_argument("a sub-layer's role is 'mixer' or 'feed_forward', not '" + s.role + "'");
                 if (s.norm_placement != "pre" && s.norm_placement != "post") throw std::invalid_argument("norm_placement is 'pre' or 'post'");
                 mixers += s.role == "mixer";
-                if (s.shift.present && (l.parallel || s.role != "mixer" || s.norm_placement != "pre"))
-                    throw std::invalid_argument("a shift stands in front of a mixer, behind a norm in front of it, in a layer that is not parallel");
-                if (l.parallel && (!s.norm.present || s.norm_placement != "pre" || s.output_norm.present))
-                    throw std::invalid_argument("a parallel layer's sub-layers each have a norm in front and none behind");
+                const bool grouped = i < group;
+                if (s.shift.present && (s.role != "mixer" || s.norm_placement != "pre" || !s.norm.present || (grouped && i != 0)))
+                    throw std::invalid_argument("a shift stands in front of a mixer, behind a norm in front of it (in a parallel group: in its first sub-layer)");
+                if (grouped && s.norm_placement != "pre") throw std::invalid_argument("a parallel layer's sub-layers have no norm behind them");
+                if (grouped && !s.norm.present && i != 1) throw std::invalid_argument("only the second sub-layer of a parallel group may share the first one's norm");
             }
             if (mixers > 1) throw std::invalid_argument("a layer has at most one mixer");
         }

@@ -153,8 +153,7 @@ private:
             else if (dt->string == "I64") { t.dtype = Stored::I64; elem = 8; }
             else throw SafetensorsError("tensor '" + name + "': Unsupported dtype " + dt->string);
             const json::Value* shape = meta.find("shape");
-            if (!shape || !shape->is_array() || shape->array.empty())
-                throw SafetensorsError("tensor '" + name + "': missing or empty shape (scalars are not supported)");
+            if (!shape || !shape->is_array()) throw SafetensorsError("tensor '" + name + "': missing shape");      // an empty shape is a single number
             for (auto& s : shape->array) {
                 if (!s.is_number() || !s.is_integer || s.integer <= 0)
                     throw SafetensorsError("tensor '" + name + "': bad dimension in shape " + shape_text(*shape));
@@ -198,6 +197,10 @@ struct TensorRequest {
     static TensorRequest matrix(const std::string& name, long long rows, long long cols) { return {name, {{rows, cols}}, false}; }
     // a [n, 1] vector is accepted like [n] (src/models/model_param_validation.cpp:62-74)
     static TensorRequest vector(const std::string& name, long long n) { return {name, {{n}, {n, 1}}, false}; }
+    // a single number: stored without dimensions, or as [1]
+    static TensorRequest scalar(const std::string& name) { return {name, {{}, {1}}, false}; }
+    // accepted in any shape if the file has it, and never read (a tensor of a part that this model leaves out)
+    static TensorRequest ignored(const std::string& name) { return {name, {}, true}; }
 };
 
 inline std::string shape_list(const std::vector<long long>& s) {
@@ -217,7 +220,7 @@ inline void check_manifest(const std::vector<TensorRequest>& requests, const Saf
             if (!r.optional) missing.push_back(r.name);
             continue;
         }
-        if (std::find(r.shapes.begin(), r.shapes.end(), t->shape) == r.shapes.end()) {
+        if (!r.shapes.empty() && std::find(r.shapes.begin(), r.shapes.end(), t->shape) == r.shapes.end()) {
             std::string expected;
             for (size_t i = 0; i < r.shapes.size(); ++i) expected += (i ? " or " : "") + shape_list(r.shapes[i]);
             wrong.push_back("Invalid tensor shape for key '" + r.name + "': expected " + expected + ", got " + shape_list(t->shape));

@@ -90,7 +90,9 @@ struct Params {
     const float* gain_out;       //   the following norm's gain
     bf16* xn_out;                //   bfloat16(gain_out * v) [M, N]
     float* ss_out;               //   [gridDim.x][padded tokens]
-    // EPI_STORE with an activation on the way out: act(z) = act_a z^2 + z / 2 for z > 0, act_b (e^z - 1 - z) + z / 2 below
+    // EPI_STORE with an activation on the way out: act 1: act(z) = act_a z^2 + z / 2 for z > 0, act_b (e^z - 1 - z) + z / 2
+    // below; act 2: act(z) = max(z, 0)^2.  EPI_SWIGLU with act 3: g = min(gate, act_a), u = clamp(up, -act_a, act_a),
+    // out = g sigmoid(1.702 g) (u + 1)
     int act;
     float act_a, act_b;
     const void* prefetch;        // weights of a kernel that runs soon: pulled into L2 meanwhile
@@ -502,7 +504,8 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             const int n = n0 + r;
             if (n >= p.N) continue;
             float v = value(r, m);
-            if (EPI == EPI_STORE && p.act) v = v > 0.f ? fmaf(p.act_a * v, v, 0.5f * v) : fmaf(p.act_b, expm1f(v) - v, 0.5f * v);
+            if (EPI == EPI_STORE && p.act == 1) v = v > 0.f ? fmaf(p.act_a * v, v, 0.5f * v) : fmaf(p.act_b, expm1f(v) - v, 0.5f * v);
+            if (EPI == EPI_STORE && p.act == 2) v = v > 0.f ? v * v : 0.f;
             if (EPI == EPI_F32) p.out_f32[(size_t)m * p.ldo + n] = v;
             else p.out[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
         }
@@ -512,7 +515,13 @@ __global__ void __launch_bounds__(MAX_THREADS) skinny_kernel(const Params p) {
             const int m = e / half, i = e % half;
             const int n = n0 + 2 * i;
             if (n + 1 >= p.N) continue;
-            const float g = value(2 * i, m), u = value(2 * i + 1, m);
+            float g = value(2 * i, m), u = value(2 * i + 1, m);
+            if (p.act == 3) {                                         // the clamped gate: limit in act_a
+                g = fminf(g, p.act_a);
+                u = fminf(fmaxf(u, -p.act_a), p.act_a);
+                p.out[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+                continue;
+            }
             const float sig = 1.0f / (1.0f + expf(-g));
             p.out[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(u * (g * sig));
         }
@@ -750,4 +759,23 @@ EG_API int eg_gemm_skinny_xielu(cudaStream_t stream, int use_pdl, const void* W,
     return gemm_skinny_any(stream, EPI_STORE, 0, use_pdl, W, ldw, nullptr, M, N, K, x, ldx, nullptr, nullptr, nullptr, nullptr, 0.f, out, ldo, row_blocks,
                            k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
                            nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 1, act_a, act_b);
+}
+
+// out [M, N] bfloat16 = max(x W^T, 0)^2, the square applied to the finished sums.  Sizes, plan and scratch as eg_gemm_skinny
+// with a plain store.
+EG_API int eg_gemm_skinny_relu2(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx,
+                                void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status) {
+    return gemm_skinny_any(stream, EPI_STORE, 0, use_pdl, W, ldw, nullptr, M, N, K, x, ldx, nullptr, nullptr, nullptr, nullptr, 0.f, out, ldo, row_blocks,
+                           k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
+                           nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 2, 0.f, 0.f);
+}
+
+// out [M, N / 2] bfloat16 from interleaved rows of W (2i = gate_i, 2i + 1 = up_i) with the clamped gate on the finished sums:
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1).  Sizes, plan and scratch as eg_gemm_skinny.
+EG_API int eg_gemm_skinny_clamped_glu(cudaStream_t stream, int use_pdl, const void* W, long long ldw, int M, int N, int K, const void* x, long long ldx,
+                                      void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status,
+                                      float limit) {
+    return gemm_skinny_any(stream, EPI_SWIGLU, 0, use_pdl, W, ldw, nullptr, M, N, K, x, ldx, nullptr, nullptr, nullptr, nullptr, 0.f, out, ldo, row_blocks,
+                           k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
+                           nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 3, limit, 0.f);
 }

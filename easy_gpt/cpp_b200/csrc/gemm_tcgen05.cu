@@ -43,7 +43,7 @@ constexpr int THREADS = 192;                                     // 6 warps
 constexpr int TMEM_COLS = 128;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 2, EPI_XIELU = 5 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 2, EPI_XIELU = 5, EPI_RELU2 = 6 };
 
 
 // Bounded wait: false if it gave up (or another role already did).
@@ -92,6 +92,20 @@ __device__ __forceinline__ float swiglu_fast(float g, float u) {
     return u * (g * r);
 }
 
+// The gate of a gated feed-forward: limit 0: up * silu(gate); limit > 0: g = min(gate, limit), u = clamp(up, -limit, limit),
+// g * sigmoid(1.702 g) * (u + 1).
+__device__ __forceinline__ float glu_fast(float g, float u, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        float e, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.702f * 1.4426950408889634f * g));
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+        return u * (g * r);
+    }
+    return swiglu_fast(g, u);
+}
+
 // xIELU for an epilogue whose result is rounded to bfloat16: the hardware's base-2 exponent for the branch below zero.
 __device__ __forceinline__ float xielu_fast(float z, float a, float b) {
     if (z > 0.f) return fmaf(a * z, z, 0.5f * z);
@@ -124,6 +138,8 @@ struct Params {
     const int* tile_group;
     // EPI_XIELU (pair kernel): out = a z^2 + z / 2 for z > 0, b (e^z - 1 - z) + z / 2 for z <= 0, element by element
     float act_a = 0.f, act_b = 0.f;
+    // EPI_SWIGLU with glu_limit > 0: the clamped gate (glu_fast).  EPI_RELU2 (pair kernel): out = max(z, 0)^2
+    float glu_limit = 0.f;
 };
 
 __global__ void __launch_bounds__(THREADS)
@@ -230,7 +246,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                            const float y0 = swiglu_fast(g0, u0), y1 = swiglu_fast(g1, u1);
+                            const float y0 = glu_fast(g0, u0, p.glu_limit), y1 = glu_fast(g1, u1, p.glu_limit);
                             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
                             packed[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
@@ -396,7 +412,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float g0 = v[4 * j], u0 = v[4 * j + 1], g1 = v[4 * j + 2], u1 = v[4 * j + 3];
-                            const float y0 = swiglu_fast(g0, u0), y1 = swiglu_fast(g1, u1);
+                            const float y0 = glu_fast(g0, u0, p.glu_limit), y1 = glu_fast(g1, u1, p.glu_limit);
                             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
                             packed[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
@@ -642,7 +658,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         uint32_t packed[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const float y0 = swiglu_fast(v[4 * j], v[4 * j + 1]), y1 = swiglu_fast(v[4 * j + 2], v[4 * j + 3]);
+                            const float y0 = glu_fast(v[4 * j], v[4 * j + 1], p.glu_limit), y1 = glu_fast(v[4 * j + 2], v[4 * j + 3], p.glu_limit);
                             __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
                             packed[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
@@ -656,6 +672,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                         if (p.epilogue == EPI_XIELU) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = xielu_fast(v[j], p.act_a, p.act_b);
+                        }
+                        if (p.epilogue == EPI_RELU2) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] * v[j] : 0.f;
                         }
                         uint32_t packed[16];
 #pragma unroll
@@ -987,8 +1007,8 @@ EG_API int eg_gemm_tcgen05(cudaStream_t stream, int epilogue, const void* A, lon
 // a multiple of 128; row tile i (128 rows) belongs to group tile_group[i] (device array of max_rows / 128 entries; negative:
 // an empty tile) and is multiplied by that group's W (W [groups * N, K]).  out [max_rows, N] (or [max_rows, N / 2] with the
 // SwiGLU epilogue on interleaved columns), bfloat16.  One launch whatever the groups' sizes, which only the device knows.
-EG_API int eg_gemm_tcgen05_grouped(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, void* out,
-                                   long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status) {
+static int gemm_tcgen05_grouped_any(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, void* out,
+                                   long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status, float glu_limit) {
     if (max_rows <= 0 || N <= 0 || groups <= 0) return 0;
     if (max_rows % BM || N % BN || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16 ||
         (epilogue != EPI_STORE && epilogue != EPI_SWIGLU) || !status || !tile_group)
@@ -1002,9 +1022,23 @@ EG_API int eg_gemm_tcgen05_grouped(cudaStream_t stream, int epilogue, const void
         configured = true;
     }
     Params p{(bf16*)out, ldo, nullptr, max_rows, N, K, epilogue, status, nullptr, tile_group};
+    p.glu_limit = glu_limit;
     dim3 grid(N / BN, max_rows / BM);
     gemm_tcgen05_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_w, p);
     return eg_launch_status();
+}
+
+EG_API int eg_gemm_tcgen05_grouped(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw, void* out,
+                                   long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status) {
+    return gemm_tcgen05_grouped_any(stream, epilogue, A, lda, W, ldw, out, ldo, max_rows, N, K, groups, tile_group, status, 0.f);
+}
+
+// The grouped product over interleaved gate and up columns with the clamped gate in its epilogue (out [max_rows, N / 2]):
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1).
+EG_API int eg_gemm_tcgen05_grouped_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo,
+                                       int max_rows, int N, int K, int groups, const int* tile_group, int* status, float limit) {
+    if (!(limit > 0.f)) return (int)cudaErrorInvalidValue;
+    return gemm_tcgen05_grouped_any(stream, EPI_SWIGLU, A, lda, W, ldw, out, ldo, max_rows, N, K, groups, tile_group, status, limit);
 }
 
 namespace {
@@ -1077,7 +1111,7 @@ static int gemm_tcgen05_pair_any(cudaStream_t stream, int epilogue, const void* 
                                  long long* trace, float act_a, float act_b) {
     if (M <= 0 || N <= 0) return 0;
     if ((tile_n != 128 && tile_n != 256) || N % tile_n || K % BK || K <= 0 || lda % 8 || ldw % 8 || ldo % 8 || (uintptr_t)A % 16 ||
-        (uintptr_t)W % 16 || (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_XIELU) ||
+        (uintptr_t)W % 16 || (uintptr_t)out % 16 || (epilogue != EPI_STORE && epilogue != EPI_SWIGLU && epilogue != EPI_XIELU && epilogue != EPI_RELU2) ||
         (epilogue == EPI_SWIGLU && tile_n != 256) || !status)
         return (int)cudaErrorInvalidValue;
     static int sm_count = 0;
@@ -1093,13 +1127,14 @@ static int gemm_tcgen05_pair_any(cudaStream_t stream, int epilogue, const void* 
     Params p{(bf16*)out, ldo, bias, M, N, K, epilogue, status, trace};
     p.act_a = act_a;
     p.act_b = act_b;
+    if (epilogue == EPI_SWIGLU) p.glu_limit = act_a;              // the clamped gate's limit rides in act_a (0: SwiGLU)
     return tile_n == 256 ? launch_pair<256>(stream, map_a, map_w, map_out, p, sm_count) : launch_pair<128>(stream, map_a, map_w, map_out, p, sm_count);
 }
 
 EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A, long long lda, const void* W, long long ldw,
                                 const float* bias, void* out, long long ldo, int M, int N, int K, int tile_n, int* status,
                                 long long* trace) {
-    if (epilogue == EPI_XIELU) return (int)cudaErrorInvalidValue;
+    if (epilogue == EPI_XIELU || epilogue == EPI_RELU2) return (int)cudaErrorInvalidValue;
     return gemm_tcgen05_pair_any(stream, epilogue, A, lda, W, ldw, bias, out, ldo, M, N, K, tile_n, status, trace, 0.f, 0.f);
 }
 
@@ -1108,4 +1143,18 @@ EG_API int eg_gemm_tcgen05_pair(cudaStream_t stream, int epilogue, const void* A
 EG_API int eg_gemm_tcgen05_pair_xielu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M,
                                       int N, int K, int tile_n, int* status, float act_a, float act_b) {
     return gemm_tcgen05_pair_any(stream, EPI_XIELU, A, lda, W, ldw, nullptr, out, ldo, M, N, K, tile_n, status, nullptr, act_a, act_b);
+}
+
+// The same product with a squared ReLU in its epilogue: out = max(A W^T, 0)^2, bfloat16 [M, N].
+EG_API int eg_gemm_tcgen05_pair_relu2(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M,
+                                      int N, int K, int tile_n, int* status) {
+    return gemm_tcgen05_pair_any(stream, EPI_RELU2, A, lda, W, ldw, nullptr, out, ldo, M, N, K, tile_n, status, nullptr, 0.f, 0.f);
+}
+
+// The same product over interleaved gate and up columns with the clamped gate in its epilogue, out bfloat16 [M, N / 2]:
+// g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1).  Tiles of 256 x 256.
+EG_API int eg_gemm_tcgen05_pair_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M,
+                                    int N, int K, int* status, float limit) {
+    if (!(limit > 0.f)) return (int)cudaErrorInvalidValue;
+    return gemm_tcgen05_pair_any(stream, EPI_SWIGLU, A, lda, W, ldw, nullptr, out, ldo, M, N, K, 256, status, nullptr, limit, 0.f);
 }

@@ -17,6 +17,11 @@
 //   eg_moe_gather    out[t, :] = sum_k weight[t, k] * (y[row_of[t, k], :] or h[t, :]) + g[t] * shared[t, :]
 // The sizes of the runs stay on the device: nothing here waits for the host.
 // Products accumulate in float32; the router is float32 throughout.
+//
+// Variants, each a parameter: `scoring` 1 takes s = sigmoid(logits) instead of the softmax (the correction may then be null);
+// `activation` 1 is the clamped gate g' = min(g, limit), u' = clamp(u, -limit, limit), a = g' sigmoid(1.702 g') (u' + 1);
+// `input_weights` (eg_moe_hidden, eg_moe_dispatch) multiply an expert's INPUT row, expert(w h), and eg_moe_combine / eg_moe_gather
+// then get null weights (every term counts once); a null gate adds the shared expert's output as it is.
 #include "common.cuh"
 
 namespace {
@@ -44,17 +49,21 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h
 
 // a warp per token: softmax over the logits (left in place as scores), then the `top` largest of score + correction
 __global__ void __launch_bounds__(128) moe_select_kernel(float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
-                                                         float* __restrict__ weights, int tokens, int outputs, int top) {
+                                                         float* __restrict__ weights, int tokens, int outputs, int top, int scoring) {
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= tokens) return;
     float* logit = logits + (size_t)t * outputs;
-    float top_logit = -INFINITY;
-    for (int e = lane; e < outputs; e += 32) top_logit = fmaxf(top_logit, logit[e]);
-    top_logit = warp_max(top_logit);
-    float sum = 0.f;
-    for (int e = lane; e < outputs; e += 32) sum += expf(logit[e] - top_logit);
-    sum = warp_sum(sum);
-    for (int e = lane; e < outputs; e += 32) logit[e] = expf(logit[e] - top_logit) / sum;      // now the scores s
+    if (scoring == 1) {
+        for (int e = lane; e < outputs; e += 32) logit[e] = 1.0f / (1.0f + expf(-logit[e]));      // now the scores s
+    } else {
+        float top_logit = -INFINITY;
+        for (int e = lane; e < outputs; e += 32) top_logit = fmaxf(top_logit, logit[e]);
+        top_logit = warp_max(top_logit);
+        float sum = 0.f;
+        for (int e = lane; e < outputs; e += 32) sum += expf(logit[e] - top_logit);
+        sum = warp_sum(sum);
+        for (int e = lane; e < outputs; e += 32) logit[e] = expf(logit[e] - top_logit) / sum;      // now the scores s
+    }
     __syncwarp();
     unsigned long long taken = 0ull;             // a lane tracks which of its own outputs are taken: bit k for e = lane + 32 k
     for (int k = 0; k < top; ++k) {
@@ -62,7 +71,7 @@ __global__ void __launch_bounds__(128) moe_select_kernel(float* __restrict__ log
         int arg = 0x7fffffff;
         for (int e = lane, i = 0; e < outputs; e += 32, ++i) {
             if ((taken >> i) & 1ull) continue;
-            const float v = logit[e] + correction[e];
+            const float v = logit[e] + (correction ? correction[e] : 0.f);
             if (v > best) { best = v; arg = e; }
         }
         for (int o = 16; o > 0; o >>= 1) {
@@ -82,7 +91,8 @@ __global__ void __launch_bounds__(128) moe_select_kernel(float* __restrict__ log
 // 2 f and its up row at 2 f + 1
 template <typename T>
 __global__ void __launch_bounds__(256) moe_hidden_kernel(const T* __restrict__ h, long long ld, const T* __restrict__ GU, const int* __restrict__ ids,
-                                                         T* __restrict__ act, int width, int ff, int top, int experts) {
+                                                         const float* __restrict__ input_weights, T* __restrict__ act, int width, int ff, int top,
+                                                         int experts, int activation, float limit) {
     extern __shared__ float row[];
     const int t = blockIdx.x, k = blockIdx.y;
     const int e = ids[(size_t)t * top + k];
@@ -120,7 +130,20 @@ __global__ void __launch_bounds__(256) moe_hidden_kernel(const T* __restrict__ h
     }
     ag = warp_sum(ag);
     au = warp_sum(au);
-    if (lane == 0) act[((size_t)t * top + k) * ff + f] = from_f32<T>(ag / (1.0f + expf(-ag)) * au);
+    if (input_weights) {                                         // the expert reads w h: its two products are w times these
+        const float wgt = input_weights[(size_t)t * top + k];
+        ag *= wgt;
+        au *= wgt;
+    }
+    float a;
+    if (activation == 1) {
+        ag = fminf(ag, limit);
+        au = fminf(fmaxf(au, -limit), limit);
+        a = ag / (1.0f + expf(-1.702f * ag)) * (au + 1.0f);
+    } else {
+        a = ag / (1.0f + expf(-ag)) * au;
+    }
+    if (lane == 0) act[((size_t)t * top + k) * ff + f] = from_f32<T>(a);
 }
 
 // grid (token, chunk of width); a warp per output value; Dn [experts, width, ff]
@@ -136,7 +159,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         const int e = ids[(size_t)t * top + k];
-        const float wgt = weights[(size_t)t * top + k];
+        const float wgt = weights ? weights[(size_t)t * top + k] : 1.0f;
         if (e >= experts) {
             total += wgt * to_f32<T>(h[(size_t)t * ld + j]);
             continue;
@@ -166,7 +189,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
     }
     if (shared) {
         const size_t i = (size_t)t * width + j;
-        total += gate[t] * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
+        total += (gate ? gate[t] : 1.0f) * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
     }
     if (lane == 0) out[(size_t)t * width + j] = total;
 }
@@ -176,25 +199,25 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ 
 // ids [T, top] int32 (router outputs; those >= the number of experts stand for the identity), weights [T, top] float32,
 // gate [T] float32 (only with gate_w); logits [T, outputs] float32 is scratch (it ends up holding the scores)
 EG_API int eg_moe_route(cudaStream_t stream, int dtype, const void* h, long long ld, const float* router, const float* correction, const float* gate_w,
-                        float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top) {
+                        float* logits, int* ids, float* weights, float* gate, int tokens, int width, int outputs, int top, int scoring) {
     if (tokens <= 0) return 0;
-    if (top < 1 || top > outputs || outputs > 2048 || !logits) return (int)cudaErrorInvalidValue;
+    if (top < 1 || top > outputs || outputs > 2048 || !logits || scoring < 0 || scoring > 1) return (int)cudaErrorInvalidValue;
     dim3 grid(tokens, (outputs + (gate_w ? 1 : 0) + 7) / 8);
     if (dtype == EG_BF16) moe_logits_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)h, ld, router, gate_w, logits, gate, width, outputs);
     else moe_logits_kernel<float><<<grid, 256, 0, stream>>>((const float*)h, ld, router, gate_w, logits, gate, width, outputs);
-    moe_select_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(logits, correction, ids, weights, tokens, outputs, top);
+    moe_select_kernel<<<(tokens + 3) / 4, 128, 0, stream>>>(logits, correction, ids, weights, tokens, outputs, top, scoring);
     return eg_launch_status();
 }
 
 // act [T, top, ff] in the compute dtype; rows of identity choices (ids >= experts) are left untouched
-EG_API int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, void* act, int tokens,
-                         int width, int ff, int top, int experts) {
+EG_API int eg_moe_hidden(cudaStream_t stream, int dtype, const void* h, long long ld, const void* gate_up, const int* ids, const float* input_weights,
+                         void* act, int tokens, int width, int ff, int top, int experts, int activation, float limit) {
     if (tokens <= 0 || experts <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     dim3 grid(tokens, top, (ff + 7) / 8);
-    if (dtype == EG_BF16) moe_hidden_kernel<bf16><<<grid, 256, smem, stream>>>((const bf16*)h, ld, (const bf16*)gate_up, ids, (bf16*)act, width, ff, top, experts);
-    else moe_hidden_kernel<float><<<grid, 256, smem, stream>>>((const float*)h, ld, (const float*)gate_up, ids, (float*)act, width, ff, top, experts);
+    if (dtype == EG_BF16) moe_hidden_kernel<bf16><<<grid, 256, smem, stream>>>((const bf16*)h, ld, (const bf16*)gate_up, ids, input_weights, (bf16*)act, width, ff, top, experts, activation, limit);
+    else moe_hidden_kernel<float><<<grid, 256, smem, stream>>>((const float*)h, ld, (const float*)gate_up, ids, input_weights, (float*)act, width, ff, top, experts, activation, limit);
     return eg_launch_status();
 }
 
@@ -238,8 +261,8 @@ __global__ void moe_offsets_kernel(const int* __restrict__ counts, int* __restri
 }
 // a warp per (token, choice): takes the next row of the expert's run and copies the token's row there
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const bf16* __restrict__ h, long long ld, const int* __restrict__ ids, const int* __restrict__ starts,
-                                                          int* __restrict__ cursors, int* __restrict__ row_of, bf16* __restrict__ rows, int pairs, int width,
-                                                          int top, int experts, int max_rows) {
+                                                          int* __restrict__ cursors, int* __restrict__ row_of, bf16* __restrict__ rows,
+                                                          const float* __restrict__ input_weights, int pairs, int width, int top, int experts, int max_rows) {
     const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (pair >= pairs) return;
     const int e = ids[pair];
@@ -257,7 +280,10 @@ __global__ void __launch_bounds__(256) moe_scatter_kernel(const bf16* __restrict
     if (row < 0) return;
     const bf16* src = h + (size_t)(pair / top) * ld;
     bf16* dst = rows + (size_t)row * width;
-    if (width % 8 == 0 && ld % 8 == 0) {
+    if (input_weights) {                                        // the expert's input is the row times the pair's weight
+        const float wgt = input_weights[pair];
+        for (int j = lane; j < width; j += 32) dst[j] = __float2bfloat16_rn(wgt * __bfloat162float(src[j]));
+    } else if (width % 8 == 0 && ld % 8 == 0) {
         for (int j = lane; j < width / 8; j += 32) reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(src)[j];
     } else {
         for (int j = lane; j < width; j += 32) dst[j] = src[j];
@@ -272,14 +298,14 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ y, const int* __restr
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         const int e = ids[(size_t)t * top + k];
-        const float wgt = weights[(size_t)t * top + k];
+        const float wgt = weights ? weights[(size_t)t * top + k] : 1.0f;
         if (e >= experts) total += wgt * __bfloat162float(h[(size_t)t * ld + j]);
         else {
             const int row = row_of[(size_t)t * top + k];
             if (row >= 0) total += wgt * __bfloat162float(y[(size_t)row * width + j]);
         }
     }
-    if (shared) total += gate[t] * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
+    if (shared) total += (gate ? gate[t] : 1.0f) * (shared_dtype == EG_BF16 ? __bfloat162float(((const bf16*)shared)[i]) : ((const float*)shared)[i]);
     out[i] = total;
 }
 }  // namespace
@@ -287,8 +313,8 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ y, const int* __restr
 // Sorts the step's (token, choice) pairs by expert (bfloat16 rows).  counts, cursors [experts] and starts [experts + 1] are
 // scratch; tile_group [max_rows / 128] and row_of [tokens * top] are results, rows [max_rows, width] receives the copies.
 // max_rows: a multiple of 128, at least tokens * top rounded up to 128 plus 128 per expert.
-EG_API int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, int* counts, int* starts, int* cursors, int* tile_group,
-                           int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows) {
+EG_API int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, const int* ids, const float* input_weights, int* counts, int* starts, int* cursors,
+                           int* tile_group, int* row_of, void* rows, int tokens, int width, int top, int experts, int max_rows) {
     const int pairs = tokens * top;
     if (pairs <= 0 || experts <= 0) return 0;
     if (max_rows % 128 || max_rows < (pairs + 127) / 128 * 128 + 128 * experts || experts > 2048) return (int)cudaErrorInvalidValue;
@@ -296,7 +322,7 @@ EG_API int eg_moe_dispatch(cudaStream_t stream, const void* h, long long ld, con
     if (e != cudaSuccess) return (int)e;
     moe_count_kernel<<<(pairs + 255) / 256, 256, 0, stream>>>(ids, counts, pairs, experts);
     moe_offsets_kernel<<<1, 256, 0, stream>>>(counts, starts, cursors, tile_group, experts, max_rows / 128);
-    moe_scatter_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>((const bf16*)h, ld, ids, starts, cursors, row_of, (bf16*)rows, pairs, width, top, experts, max_rows);
+    moe_scatter_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>((const bf16*)h, ld, ids, starts, cursors, row_of, (bf16*)rows, input_weights, pairs, width, top, experts, max_rows);
     return eg_launch_status();
 }
 
