@@ -112,6 +112,25 @@ def lasizen_bench_configs(size):
     return lasizen, qwen
 
 
+# Layer sizes for `--only masezen`: attention of 16 heads of 128 over 4 key heads whose scores are mixed across the heads (the
+# keys are the values), four taps of convolution in front of it, a per-layer token input of 64 values, and six layers: a dense
+# squared-ReLU feed-forward of 1.5 times the width, then two layers of 16 routed experts of 512 of which a token takes two beside a
+# shared one of 1,024, twice ("medium"); half of the width, heads and feed-forwards ("small").  The Qwen2 decoder beside it has the
+# same width, layers and heads and a SwiGLU feed-forward with as many weights as a Masezen layer uses per token.
+def masezen_bench_configs(size):
+    k = {"medium": 1, "small": 2}[size]
+    width, heads, ff = 2048 // k, 16 // k, 512 // k
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                                "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    dense = {"kind": "dense", "ff": 6 * ff}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": 2 * ff, "limit": 7.0}}
+    masezen = {"architecture": "Masezen", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "token_side": {"dim": 64 // k},
+               "layers": [dict(attention, mlp=m) for m in (dense, moe, moe, dense, moe, moe)]}
+    qwen = dict(CONFIG_05B, num_hidden_layers=6, hidden_size=width, num_attention_heads=heads, num_key_value_heads=4 // k, head_dim=128,
+                intermediate_size=4 * ff, vocab_size=32000, tie_word_embeddings=False)
+    return masezen, qwen
+
+
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -295,6 +314,8 @@ def gufanex_folder(config, seed=0):
 
     if config.get("architecture") == "Lasizen":
         from easy_gpt.cpp_b200.weights.lasizen_init import write_random_model
+    elif config.get("architecture") == "Masezen":
+        from easy_gpt.cpp_b200.weights.masezen_init import write_random_model
     else:
         from easy_gpt.cpp_b200.weights.gufanex_init import write_random_model
 
@@ -625,9 +646,27 @@ def run_lasizen(args):
     return 0
 
 
+def run_masezen(args):
+    size = args.sizes if args.sizes in ("small", "medium") else "medium"
+    masezen, qwen = masezen_bench_configs(size)
+    context = min(args.context, 2048) if args.context == CONTEXT else args.context
+    out = {"only": "masezen", "sizes": size, "batch": args.batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bfloat16",
+           "data": "synthetic (random weights)"}
+    with ClockSampler() as clocks:
+        if args.model in ("both", "masezen"):
+            out["masezen"] = measure_prefill_and_decode(gufanex_folder(masezen), masezen["vocab"], args.batch, context, args.steps, args.warmup)
+        if args.model in ("both", "qwen2"):
+            out["qwen2_equal"] = measure_prefill_and_decode(model_folder(qwen), qwen["vocab_size"], args.batch, context, args.steps, args.warmup)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
     if args.only == "gufanex":
         return run_gufanex(args)
+    if args.only == "masezen":
+        return run_masezen(args)
     if args.only == "lasizen":
         return run_lasizen(args)
     config = dict(CONFIG_05B, **SIZES[args.sizes])
@@ -757,16 +796,16 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
-    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex and --only lasizen)")
-    ap.add_argument("--model", choices=["both", "gufanex", "lasizen", "qwen2"], default="both",
-                    help="with --only gufanex or --only lasizen: which of the two models to measure")
+    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex, --only lasizen and --only masezen)")
+    ap.add_argument("--model", choices=["both", "gufanex", "lasizen", "masezen", "qwen2"], default="both",
+                    help="with --only gufanex, --only lasizen or --only masezen: which of the two models to measure")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="precision of --only decode")
     ap.add_argument("--default-options", action="store_true",
                     help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex", "lasizen"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex", "lasizen", "masezen"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:

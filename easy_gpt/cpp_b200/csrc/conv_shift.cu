@@ -27,7 +27,7 @@ __global__ void conv_shift_kernel(const float* __restrict__ rows, const float* _
     __shared__ float inv[MAX_TAPS];
     const int t = blockIdx.x, seq = token_seq[t], start = seq_starts[seq];
     const int back = min(taps - 1, t - start);                  // earlier rows that lie in this step
-    const float* slot = state + (size_t)seq_slots[seq] * slot_floats;
+    const float* slot = taps > 1 ? state + (size_t)seq_slots[seq] * slot_floats : nullptr;      // one tap: no earlier rows, no slot
     for (int d = 0; d <= back; ++d) {
         float r = 1.0f;
         if (!NORMED) {

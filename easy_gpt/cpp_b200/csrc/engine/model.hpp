@@ -113,7 +113,8 @@ public:
             if (i == 0) {
                 const bool shares = group >= 2 && !sublayers[1].norm;          // the second sub-layer reads this norm's rows
                 if (sub.shift) {
-                    if (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()) throw DeviceError("a shift was handed no state of its size");
+                    if (sub.shift->state_floats() > 0 && (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()))
+                        throw DeviceError("a shift was handed no state of its size");
                     settle(ctx, s, n, true);
                     const float* gain = nullptr;
                     float eps = 0.f;
@@ -249,7 +250,8 @@ public:
             } else if (sub.shift) {
                 // norm, then the mix with the row in front: one kernel where the norm is a plain RMSNorm, else the normed
                 // rows in float32 and the shift behind them
-                if (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()) throw DeviceError("a shift was handed no state of its size");
+                if (sub.shift->state_floats() > 0 && (!cache.layer_state || cache.layer_state_floats < sub.shift->state_floats()))
+                        throw DeviceError("a shift was handed no state of its size");
                 const float* gain = nullptr;
                 float eps = 0.f;
                 if (!(sub.norm->rms_parameters(&gain, &eps) &&
