@@ -131,6 +131,12 @@ int eg_conv_shift_state(cudaStream_t stream, const float* rows, const float* gai
 int eg_mixed_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* q_weight, const float* k_weight, float eps, const float* table, int rot_dims, float magnitude, const float* mix, float scale, const int* slot_map, void* k_cache, void* v_cache, long long head_stride, int page_size, long long page_stride, long long pool_slots, void* q_out, int q_dtype, int tokens, int heads, int kv_heads, int dk, int* status);
 // attention_mixed.cu
 int eg_mixed_attention(cudaStream_t stream, int dtype, const void* q, int q_dtype, const void* k_cache, const void* v_cache, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const float* gate, long long ld_gate, void* out, long long ldo, int num_tokens, int heads, int kv_heads, int dk, int page_size, long long page_stride, int num_pages, int* status);
+// attention_mixed_mma.cu
+int eg_mixed_attention_mma_takes(int heads, int kv_heads, int dk);
+// attention_mixed_mma.cu
+int eg_mixed_attention_tiles(cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache, long long head_stride, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, const float* gate, long long ld_gate, void* out, long long ldo, int heads, int kv_heads, int dk, int page_size, long long page_stride, int num_pages, int* status);
+// attention_mixed_mma.cu
+int eg_mixed_attention_split(cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, int num_tokens, const float* gate, long long ld_gate, void* out, long long ldo, float* partial_acc, float* partial_ml, int splits, int heads, int kv_heads, int dk, int page_size, long long page_stride, int num_pages, int* status);
 // token_side.cu
 int eg_token_side(cudaStream_t stream, int dtype, float* residual, const void* delta_a, int dtype_a, const float* scale_a, const void* delta_b, int dtype_b, const float* scale_b, const int* token_ids, const void* table, int vocab, const void* gate_w, const void* proj_w, const float* norm_gain, float eps, int tokens, int hidden, int side, int* status);
 // token_side.cu

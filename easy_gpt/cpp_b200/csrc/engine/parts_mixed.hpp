@@ -112,7 +112,9 @@ public:
     }
     size_t weight_bytes() const override { return in_.weight_bytes() + out_.weight_bytes() + (size_t)heads_ * heads_ * 4; }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)heads_ * kv_heads_ * dk_ * 4 + (size_t)heads_ * dk_ * 4 + (size_t)hidden_ * 4) + (1u << 16);
+        // a step of single tokens keeps per-range sums: fewer than 2 SPLIT_CTAS (token, 16 heads, range) triples
+        const size_t ranges = (size_t)2 * SPLIT_CTAS * 16 * (dk_ + 2) * 4;
+        return (size_t)T * ((size_t)in_.out_features * 4 + (size_t)heads_ * kv_heads_ * dk_ * 4 + (size_t)heads_ * dk_ * 4 + (size_t)hidden_ * 4) + ranges + (1u << 16);
     }
     bool capturable() const override { return true; }
     CacheNeed cache_need() const override { return CacheNeed::paged(kv_heads_, dk_, -1); }
@@ -130,7 +132,10 @@ public:
         if (rotates && rot.rotary_dim > dk_) throw DeviceError("mixed attention: the rotation covers more than a head");
         const float* table = rotates ? step_rotation_table(ctx, rot) : nullptr;
         const int wide = kv_heads_ * dk_;
-        const DType q_dtype = DType::F32;
+        // bfloat16 steps of sizes the tensor-core kernels take: folded queries in bfloat16, prompt portions by tiles, single
+        // tokens split over their keys; everything else (and float32) through the generic kernel with float32 queries
+        const bool mma = dtype == DType::BF16 && eg_mixed_attention_mma_takes(heads_, kv_heads_, dk_);
+        const DType q_dtype = mma ? DType::BF16 : DType::F32;
         void* q = ctx.take_rows(T, (size_t)heads_ * wide, q_dtype);
         launch_check(eg_mixed_attention_prepare(ctx.stream, (int)dtype, (const float*)proj.p, proj.ld, q_weight_.as<float>(), k_weight_.as<float>(), norm_eps_, table,
                                                 rotates ? rot.rotary_dim : 0, rot.magnitude, mix_.as<float>(), scale_, tables.slot_map,
@@ -139,9 +144,29 @@ public:
                      "mixed_attention_prepare");
         Rows attn{ctx.take_rows(T, heads_ * dk_, dtype), dtype, T, heads_ * dk_, heads_ * dk_};
         const float* gate = (const float*)proj.p + (size_t)(heads_ + kv_heads_) * dk_;
-        launch_check(eg_mixed_attention(ctx.stream, (int)dtype, q, (int)q_dtype, cache.k, cache.v, cache.head_stride, tables.block_table, tables.table_width,
-                                        ctx.token_seq, ctx.positions, gate, proj.ld, attn.p, attn.ld, T, heads_, kv_heads_, dk_, cache.page_size, cache.page_stride,
-                                        cache.num_pages, ctx.status), "mixed_attention");
+        if (mma) {
+            if (ctx.query_tiles)
+                launch_check(eg_mixed_attention_tiles(ctx.stream, q, cache.k, cache.v, cache.head_stride, tables.block_table, tables.table_width, ctx.positions,
+                                                      ctx.query_tiles, ctx.num_tiles, gate, proj.ld, attn.p, attn.ld, heads_, kv_heads_, dk_, cache.page_size,
+                                                      cache.page_stride, cache.num_pages, ctx.status), "mixed_attention_tiles");
+            const int singles = ctx.query_tiles ? ctx.num_small : T;
+            if (singles > 0) {
+                const int splits = split_plan(singles, heads_, ctx.max_context_len);
+                float *acc = nullptr, *ml = nullptr;
+                if (splits > 1) {
+                    acc = ctx.take<float>((size_t)singles * heads_ * splits * dk_);
+                    ml = ctx.take<float>((size_t)singles * heads_ * splits * 2);
+                }
+                launch_check(eg_mixed_attention_split(ctx.stream, q, cache.k, cache.v, cache.head_stride, tables.block_table, tables.table_width, ctx.token_seq,
+                                                      ctx.positions, ctx.query_tiles ? ctx.small_tokens : nullptr, singles, gate, proj.ld, attn.p, attn.ld, acc, ml,
+                                                      splits, heads_, kv_heads_, dk_, cache.page_size, cache.page_stride, cache.num_pages, ctx.status),
+                             "mixed_attention_split");
+            }
+        } else {
+            launch_check(eg_mixed_attention(ctx.stream, (int)dtype, q, (int)q_dtype, cache.k, cache.v, cache.head_stride, tables.block_table, tables.table_width,
+                                            ctx.token_seq, ctx.positions, gate, proj.ld, attn.p, attn.ld, T, heads_, kv_heads_, dk_, cache.page_size,
+                                            cache.page_stride, cache.num_pages, ctx.status), "mixed_attention");
+        }
         const Rows o = out_(ctx, attn, /*out_f32=*/true);
         Delta d;
         d.p = o.p;
@@ -150,6 +175,15 @@ public:
     }
 
 private:
+    static constexpr int SPLIT_CTAS = 296;         // two CTAs a multiprocessor are what a step of single tokens is cut for
+    static constexpr int MAX_SPLITS = 64;
+    // ranges of at least 128 keys, as many as fill the GPU with the step's (token, 16 heads) pairs
+    static int split_plan(int tokens, int heads, long long longest) {
+        const long long pairs = (long long)tokens * ((heads + 15) / 16);
+        const long long wanted = (SPLIT_CTAS + pairs - 1) / pairs, useful = (std::max<long long>(longest, 1) + 127) / 128;
+        return (int)std::max<long long>(1, std::min<long long>({wanted, useful, (long long)MAX_SPLITS}));
+    }
+
     int hidden_, heads_, kv_heads_, dk_;
     float scale_, norm_eps_;
     Linear in_, out_;
