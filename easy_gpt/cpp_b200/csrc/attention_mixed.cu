@@ -15,13 +15,16 @@
 //                                queries Q [tokens, H, G * dk], and the token's k^ and k rows in the cache
 //   eg_mixed_attention           the attention over the paged cache, a warp per (token, head), float32 sums in chunks of 32
 //                                keys from position 0: the order of the sums depends on the token's position alone
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
 constexpr int WARPS = 4;
 constexpr int MAX_PER_LANE = 8;      // dk <= 256
 
-// one block per token; proj float32 [tokens, ld]: H query heads, then G key heads
+// blocks (t, y): every block norms and turns token t's heads, block y == 0 stores the keys, and the blocks share the
+// token's folded queries; proj float32 [tokens, ld]: H query heads, then G key heads
 template <typename T>
 __global__ void __launch_bounds__(256) mixed_prepare_kernel(const float* __restrict__ proj, long long ld, const float* __restrict__ q_weight,
                                                             const float* __restrict__ k_weight, float eps, const float2* __restrict__ table, int half,
@@ -38,7 +41,7 @@ __global__ void __launch_bounds__(256) mixed_prepare_kernel(const float* __restr
         const float* weight = is_q ? q_weight : k_weight;
         T *k_dst = nullptr, *v_dst = nullptr;
         if (!is_q) {
-            if (!k_cache) continue;
+            if (!k_cache || blockIdx.y != 0) continue;
             const long long slot = slot_map[t];
             if (slot < 0 || slot >= pool_slots) {
                 if (lane == 0) atomicOr(status, EG_STATUS_BAD_SLOT);
@@ -72,14 +75,32 @@ __global__ void __launch_bounds__(256) mixed_prepare_kernel(const float* __restr
         }
     }
     __syncthreads();
-    // the folded queries: head h, key head c, value d
+    // the folded queries: a warp per (head h, key head c), over all blocks of the token; a lane takes pairs of values
     const int group = heads / kv_heads, wide = kv_heads * dk;
-    for (int i = threadIdx.x; i < heads * wide; i += blockDim.x) {
-        const int h = i / wide, c = (i % wide) / dk, d = i % dk;
-        float acc = 0.f;
-        for (int g = c * group; g < (c + 1) * group; ++g) acc = fmaf(mix[h * heads + g], qs[g * dk + d], acc);
-        if (q_f32) ((float*)q_out)[(size_t)t * heads * wide + i] = acc * scale;
-        else ((bf16*)q_out)[(size_t)t * heads * wide + i] = __float2bfloat16_rn(acc * scale);
+    for (int hc = blockIdx.y * warps + warp; hc < heads * kv_heads; hc += gridDim.y * warps) {
+        const int h = hc / kv_heads, c = hc % kv_heads;
+        const float* m = mix + (size_t)h * heads + c * group;
+        const float* src = qs + (size_t)c * group * dk;
+        const size_t at = (size_t)t * heads * wide + (size_t)h * wide + (size_t)c * dk;
+        for (int d = 2 * lane; d < dk; d += 64) {
+            float a0 = 0.f, a1 = 0.f;
+            for (int g = 0; g < group; ++g) {
+                const float w = m[g];
+                a0 = fmaf(w, src[g * dk + d], a0);
+                if (d + 1 < dk) a1 = fmaf(w, src[g * dk + d + 1], a1);
+            }
+            a0 *= scale;
+            a1 *= scale;
+            if (q_f32) {
+                ((float*)q_out)[at + d] = a0;
+                if (d + 1 < dk) ((float*)q_out)[at + d + 1] = a1;
+            } else if (d + 1 < dk && dk % 2 == 0) {
+                *(__nv_bfloat162*)((bf16*)q_out + at + d) = __floats2bfloat162_rn(a0, a1);
+            } else {
+                ((bf16*)q_out)[at + d] = __float2bfloat16_rn(a0);
+                if (d + 1 < dk) ((bf16*)q_out)[at + d + 1] = __float2bfloat16_rn(a1);
+            }
+        }
     }
 }
 
@@ -172,12 +193,15 @@ EG_API int eg_mixed_attention_prepare(cudaStream_t stream, int dtype, const floa
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > dk || (rot_dims > 0 && !table) || !mix || kv_heads <= 0 || heads % kv_heads) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)heads * dk * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    // a step of few tokens spreads a token's folded queries over several blocks (each norms and turns the token's heads itself)
+    const int per_token = tokens >= 128 ? 1 : std::max(1, std::min(heads * kv_heads / 8, 128 / tokens));
+    const dim3 grid(tokens, per_token);
     if (dtype == EG_BF16)
-        mixed_prepare_kernel<bf16><<<tokens, 256, smem, stream>>>(proj, ld, q_weight, k_weight, eps, (const float2*)table, rot_dims / 2, magnitude, mix, scale, slot_map,
+        mixed_prepare_kernel<bf16><<<grid, 256, smem, stream>>>(proj, ld, q_weight, k_weight, eps, (const float2*)table, rot_dims / 2, magnitude, mix, scale, slot_map,
                                                                   (bf16*)k_cache, (bf16*)v_cache, head_stride, page_size, page_stride, pool_slots, q_out, q_dtype == EG_F32,
                                                                   heads, kv_heads, dk, status);
     else
-        mixed_prepare_kernel<float><<<tokens, 256, smem, stream>>>(proj, ld, q_weight, k_weight, eps, (const float2*)table, rot_dims / 2, magnitude, mix, scale, slot_map,
+        mixed_prepare_kernel<float><<<grid, 256, smem, stream>>>(proj, ld, q_weight, k_weight, eps, (const float2*)table, rot_dims / 2, magnitude, mix, scale, slot_map,
                                                                    (float*)k_cache, (float*)v_cache, head_stride, page_size, page_stride, pool_slots, q_out,
                                                                    q_dtype == EG_F32, heads, kv_heads, dk, status);
     return eg_launch_status();

@@ -22,7 +22,7 @@
 
 namespace {
 constexpr int THREADS = 128;
-constexpr int TILE_ROWS = 64;      // query rows a CTA of the prompt kernel holds
+constexpr int LISTED_ROWS = 128;   // tokens of a listed tile; a CTA of the prompt kernel takes 16 a warp of them
 constexpr int BN = 32;             // keys a step of the prompt kernel
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int SMEM_LIMIT = 227 * 1024;
@@ -40,6 +40,7 @@ __device__ __forceinline__ void score_tile(float (&s)[NKT][4], const bf16* q_row
     for (int i = 0; i < NKT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
     const bf16* qa = q_rows + (lane & 15) * qs + (lane >> 4) * 8;
     const bf16* kb = k_rows + ((lane >> 4) * 8 + (lane & 7)) * ks + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
     for (int k0 = 0; k0 < wide; k0 += 16) {
         uint32_t a[4];
         ldmatrix_x4(a, qa + k0);
@@ -123,21 +124,22 @@ struct TileParams {
 };
 
 // ---- prompt portions ---------------------------------------------------------------------------------------------------------
-template <int NT>
-__global__ void __launch_bounds__(THREADS) mixed_tiles_kernel(const TileParams p) {
+template <int NT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) mixed_tiles_kernel(const TileParams p) {
+    constexpr int TILE_ROWS = 16 * WARPS, SUBS = LISTED_ROWS / TILE_ROWS, NTHREADS = WARPS * 32;
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int dk = p.dk, wide = p.kv_heads * dk, qs = wide + 8, vs = dk + 8, cpr = wide / 8;
     const int sub = p.num_subtiles - 1 - (int)blockIdx.x;       // the last tiles of a prompt have the most keys: they start first
-    const int* tile = p.tiles + 3 * (sub >> 1);
-    const int first = tile[1] + TILE_ROWS * (sub & 1);
-    const int count = min(TILE_ROWS, tile[2] - TILE_ROWS * (sub & 1));
+    const int* tile = p.tiles + 3 * (sub / SUBS);
+    const int first = tile[1] + TILE_ROWS * (sub % SUBS);
+    const int count = min(TILE_ROWS, tile[2] - TILE_ROWS * (sub % SUBS));
     if (count <= 0) return;
     const int h = blockIdx.y;
     const int c_own = h / (p.heads / p.kv_heads);
     const int* table = p.block_table + (size_t)tile[0] * p.table_stride;
 
-    bf16* q_s = (bf16*)smem;                                   // [64][qs]
+    bf16* q_s = (bf16*)smem;                                   // [TILE_ROWS][qs]
     bf16* k_s = q_s + TILE_ROWS * qs;                          // [2][BN][qs]
     bf16* v_s = k_s + 2 * BN * qs;                             // [2][BN][vs]
     long long* row_off = (long long*)(v_s + 2 * BN * vs);      // [2][BN]
@@ -158,7 +160,7 @@ __global__ void __launch_bounds__(THREADS) mixed_tiles_kernel(const TileParams p
         }
     };
     auto fetch = [&](int buf) {
-        for (int j = warp; j < BN; j += THREADS / 32) {
+        for (int j = warp; j < BN; j += WARPS) {
             const long long off = row_off[buf * BN + j];
             const bool valid = off >= 0;
             bf16* kd = k_s + (buf * BN + j) * qs;
@@ -168,9 +170,9 @@ __global__ void __launch_bounds__(THREADS) mixed_tiles_kernel(const TileParams p
         }
     };
 
-    for (int cc = tid; cc < cpr; cc += THREADS) col_off[cc] = (int)(((cc * 8) / dk) * p.head_stride + (cc * 8) % dk);
+    for (int cc = tid; cc < cpr; cc += NTHREADS) col_off[cc] = (int)(((cc * 8) / dk) * p.head_stride + (cc * 8) % dk);
     find_rows(0, 0);
-    for (int i = tid; i < TILE_ROWS * cpr; i += THREADS) {
+    for (int i = tid; i < TILE_ROWS * cpr; i += NTHREADS) {
         const int r = i / cpr, cc = i % cpr;
         const bool valid = r < count;
         cp_async_16(q_s + r * qs + cc * 8, p.q + (valid ? ((size_t)(first + r) * p.heads + h) * wide + cc * 8 : 0), valid);
@@ -240,8 +242,8 @@ __global__ void __launch_bounds__(THREADS) mixed_tiles_kernel(const TileParams p
     }
 }
 
-size_t tiles_smem(int wide, int dk) {
-    return (size_t)(TILE_ROWS + 2 * BN) * (wide + 8) * 2 + (size_t)2 * BN * (dk + 8) * 2 + 2 * BN * 8 + (size_t)(wide / 8) * 4;
+size_t tiles_smem(int wide, int dk, int warps) {
+    return (size_t)(16 * warps + 2 * BN) * (wide + 8) * 2 + (size_t)2 * BN * (dk + 8) * 2 + 2 * BN * 8 + (size_t)(wide / 8) * 4;
 }
 
 // ---- single tokens -----------------------------------------------------------------------------------------------------------
@@ -430,7 +432,7 @@ static int raise_smem(K kernel, size_t bytes) {
 EG_API int eg_mixed_attention_mma_takes(int heads, int kv_heads, int dk) {
     if (!sizes_taken(heads, kv_heads, dk)) return 0;
     const int wide = kv_heads * dk;
-    return tiles_smem(wide, dk) <= (size_t)SMEM_LIMIT && split_smem(wide, padded_dk(dk)) <= (size_t)SMEM_LIMIT;
+    return tiles_smem(wide, dk, 4) <= (size_t)SMEM_LIMIT && split_smem(wide, padded_dk(dk)) <= (size_t)SMEM_LIMIT;
 }
 
 // q bfloat16 [tokens, heads, kv_heads * dk] (folded queries); tiles int32 [num_tiles, 3] = (entry, first token, count <= 128);
@@ -442,19 +444,28 @@ EG_API int eg_mixed_attention_tiles(cudaStream_t stream, const void* q, const vo
     if (!eg_mixed_attention_mma_takes(heads, kv_heads, dk)) return (int)cudaErrorInvalidValue;
     TileParams p{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, head_stride, page_stride, block_table, table_stride, positions, tiles, 2 * num_tiles,
                  gate, ld_gate, (bf16*)out, ldo, heads, kv_heads, dk, page_size, num_pages, status};
-    const size_t smem = tiles_smem(kv_heads * dk, dk);
-    const dim3 grid(2 * num_tiles, heads);
+    // eight warps (all 128 tokens of a listed tile) where their queries fit beside the keys, else four
+    const int warps = tiles_smem(kv_heads * dk, dk, 8) <= (size_t)SMEM_LIMIT ? 8 : 4;
+    const size_t smem = tiles_smem(kv_heads * dk, dk, warps);
+    const int subtiles = num_tiles * (LISTED_ROWS / (16 * warps));
+    p.num_subtiles = subtiles;
+    const dim3 grid(subtiles, heads);
     int rc = 0;
-    if (dk <= 64) {
-        if ((rc = raise_smem(mixed_tiles_kernel<8>, smem))) return rc;
-        mixed_tiles_kernel<8><<<grid, THREADS, smem, stream>>>(p);
-    } else if (dk <= 128) {
-        if ((rc = raise_smem(mixed_tiles_kernel<16>, smem))) return rc;
-        mixed_tiles_kernel<16><<<grid, THREADS, smem, stream>>>(p);
+#define EG_MIXED_TILES(NT, W)                                                   \
+    do {                                                                        \
+        if ((rc = raise_smem(mixed_tiles_kernel<NT, W>, smem))) return rc;      \
+        mixed_tiles_kernel<NT, W><<<grid, W * 32, smem, stream>>>(p);           \
+    } while (0)
+    if (warps == 8) {
+        if (dk <= 64) EG_MIXED_TILES(8, 8);
+        else if (dk <= 128) EG_MIXED_TILES(16, 8);
+        else EG_MIXED_TILES(32, 8);
     } else {
-        if ((rc = raise_smem(mixed_tiles_kernel<32>, smem))) return rc;
-        mixed_tiles_kernel<32><<<grid, THREADS, smem, stream>>>(p);
+        if (dk <= 64) EG_MIXED_TILES(8, 4);
+        else if (dk <= 128) EG_MIXED_TILES(16, 4);
+        else EG_MIXED_TILES(32, 4);
     }
+#undef EG_MIXED_TILES
     return eg_launch_status();
 }
 

@@ -17,29 +17,47 @@
 namespace {
 constexpr int MAX_TAPS = 8;
 
+// inv[d] = 1 / sqrt(mean(x_d^2) + eps) for n <= MAX_TAPS rows x_d = first + d * step (in floats) at once: one pass over the rows
+// and two barriers.  A row's sum is formed in the same order whichever of the n it is and whatever the others are.
+__device__ __forceinline__ void rows_inverse_rms(const float* first, long long step, int n, int hidden, float eps, float (*scratch)[32], float* inv) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    float ss[MAX_TAPS];
+#pragma unroll
+    for (int d = 0; d < MAX_TAPS; ++d) ss[d] = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+#pragma unroll
+        for (int d = 0; d < MAX_TAPS; ++d)
+            if (d < n) {
+                const float x = first[d * step + j];
+                ss[d] = fmaf(x, x, ss[d]);
+            }
+    }
+#pragma unroll
+    for (int d = 0; d < MAX_TAPS; ++d)
+        if (d < n) {
+            const float v = warp_sum(ss[d]);
+            if (lane == 0) scratch[d][warp] = v;
+        }
+    __syncthreads();
+    for (int d = warp; d < n; d += nwarps) {
+        const float v = warp_sum(lane < nwarps ? scratch[d][lane] : 0.f);
+        if (lane == 0) inv[d] = 1.0f / sqrtf(v / (float)hidden + eps);
+    }
+    __syncthreads();
+}
+
 // NORMED: `rows` are h already; else they are the stream and h is computed here
 template <typename TO, bool NORMED>
 __global__ void conv_shift_kernel(const float* __restrict__ rows, const float* __restrict__ gain, float eps, const float* __restrict__ w,
                                   const float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
                                   const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, TO* __restrict__ out, TO* __restrict__ plain_out,
                                   int hidden, int taps) {
-    __shared__ float scratch[32];
+    __shared__ float scratch[MAX_TAPS][32];
     __shared__ float inv[MAX_TAPS];
     const int t = blockIdx.x, seq = token_seq[t], start = seq_starts[seq];
     const int back = min(taps - 1, t - start);                  // earlier rows that lie in this step
     const float* slot = taps > 1 ? state + (size_t)seq_slots[seq] * slot_floats : nullptr;      // one tap: no earlier rows, no slot
-    for (int d = 0; d <= back; ++d) {
-        float r = 1.0f;
-        if (!NORMED) {
-            const float* x = rows + (size_t)(t - d) * hidden;
-            float ss = 0.f;
-            for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
-            ss = block_sum(ss, scratch);
-            r = 1.0f / sqrtf(ss / (float)hidden + eps);
-        }
-        if (threadIdx.x == 0) inv[d] = r;
-    }
-    __syncthreads();
+    if (!NORMED) rows_inverse_rms(rows + (size_t)t * hidden, -(long long)hidden, back + 1, hidden, eps, scratch, inv);     // inv[d]: d rows back
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         const float g = NORMED ? 1.0f : gain[j];
         float own = 0.f, acc = 0.f;
@@ -66,25 +84,14 @@ __global__ void conv_shift_kernel(const float* __restrict__ rows, const float* _
 template <bool NORMED>
 __global__ void conv_shift_state_kernel(const float* __restrict__ rows, const float* __restrict__ gain, float eps, float* __restrict__ state,
                                         long long slot_floats, const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, int hidden, int taps) {
-    __shared__ float scratch[32];
+    __shared__ float scratch[MAX_TAPS][32];
     __shared__ float inv[MAX_TAPS];
     const int seq = blockIdx.x, start = seq_starts[seq], len = seq_starts[seq + 1] - start;
     if (len <= 0) return;
     float* slot = state + (size_t)seq_slots[seq] * slot_floats;
     const int keep = taps - 1;
     const int fresh = min(keep, len);                           // the slot's last `fresh` rows come from this step
-    for (int r = 0; r < fresh; ++r) {
-        float v = 1.0f;
-        if (!NORMED) {
-            const float* x = rows + (size_t)(start + len - fresh + r) * hidden;
-            float ss = 0.f;
-            for (int j = threadIdx.x; j < hidden; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
-            ss = block_sum(ss, scratch);
-            v = 1.0f / sqrtf(ss / (float)hidden + eps);
-        }
-        if (threadIdx.x == 0) inv[r] = v;
-    }
-    __syncthreads();
+    if (!NORMED) rows_inverse_rms(rows + (size_t)(start + len - fresh) * hidden, hidden, fresh, hidden, eps, scratch, inv);
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         for (int r = 0; r < keep - fresh; ++r) slot[(size_t)r * hidden + j] = slot[(size_t)(r + fresh) * hidden + j];
         for (int r = 0; r < fresh; ++r) {

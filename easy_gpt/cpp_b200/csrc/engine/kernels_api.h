@@ -138,9 +138,9 @@ int eg_mixed_attention_tiles(cudaStream_t stream, const void* q, const void* k_c
 // attention_mixed_mma.cu
 int eg_mixed_attention_split(cudaStream_t stream, const void* q, const void* k_cache, const void* v_cache, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, int num_tokens, const float* gate, long long ld_gate, void* out, long long ldo, float* partial_acc, float* partial_ml, int splits, int heads, int kv_heads, int dk, int page_size, long long page_stride, int num_pages, int* status);
 // token_side.cu
-int eg_token_side(cudaStream_t stream, int dtype, float* residual, const void* delta_a, int dtype_a, const float* scale_a, const void* delta_b, int dtype_b, const float* scale_b, const int* token_ids, const void* table, int vocab, const void* gate_w, const void* proj_w, const float* norm_gain, float eps, int tokens, int hidden, int side, int* status);
+int eg_add_scaled_rows(cudaStream_t stream, float* residual, const void* delta_a, int dtype_a, const float* scale_a, const void* delta_b, int dtype_b, const float* scale_b, void* rows, int rows_dtype, int tokens, int hidden);
 // token_side.cu
-int eg_token_side_rows(cudaStream_t stream, int dtype, const void* rows, long long ld, float* y, const int* token_ids, const void* table, int vocab, const void* gate_w, const void* proj_w, int tokens, int hidden, int side, int* status);
+int eg_token_side_gate(cudaStream_t stream, int dtype, const float* z, long long ldz, const int* token_ids, const void* table, int vocab, void* g, int tokens, int side, int* status);
 // token_side.cu
 int eg_add_scaled(cudaStream_t stream, float* residual, const void* delta, int delta_dtype, const float* scale, int tokens, int hidden);
 // activation.cu

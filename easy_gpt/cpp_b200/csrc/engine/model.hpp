@@ -429,13 +429,16 @@ public:
                 head_dim = std::max(head_dim, hd);
             }
         }
-        size_t part_most = 0;
-        for (Part* p : all_parts()) part_most = std::max(part_most, p->arena_bytes(T));
+        size_t part_most = 0, joined_most = 0;
+        for (Part* p : all_parts()) {
+            part_most = std::max(part_most, p->arena_bytes(T));
+            joined_most = std::max(joined_most, p->joined_arena_bytes(T));
+        }
         ArenaSizes sizes;
         // partial results of an attention whose keys are shared by several CTAs: capped for prompt portions, and bounded by
         // the CTAs of a few waves for single tokens
         const size_t partials = plans::PREFILL_PARTS_SCRATCH_BYTES + (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(head_dim + 2) * 4;
-        sizes.sub = std::max((size_t)T * (size_t)widths * 4, part_most) + partials + (4u << 20);
+        sizes.sub = std::max((size_t)T * (size_t)widths * 4, part_most) + joined_most + partials + (4u << 20);
         sizes.step = (size_t)T * (size_t)(5 * spec.hidden_size + std::max<long long>(head_dim, 64)) * 4 + (size_t)R * (size_t)(spec.vocab_size + spec.hidden_size) * 4 +
                      (4u << 20);
         return sizes;

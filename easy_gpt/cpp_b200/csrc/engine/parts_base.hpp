@@ -160,6 +160,8 @@ public:
     // bytes of arena memory one forward over `tokens` tokens takes at most (0: the model's own estimate from the part's
     // parameters covers it)
     virtual size_t arena_bytes(long long /*tokens*/) const { return 0; }
+    // what the part takes from the arena of the sub-layer in front of it (a part that joins that sub-layer's outputs itself)
+    virtual size_t joined_arena_bytes(long long /*tokens*/) const { return 0; }
     // true if forward() only launches device work whose shape depends on the batch's size alone (no reads of the
     // batch's contents on the host): then decode steps may be captured in a CUDA graph
     virtual bool capturable() const { return false; }

@@ -242,7 +242,9 @@ private:
 // that all layers share.  It is gated by the stream and mapped to the model's width:
 //   y = P (gelu_tanh(G x) * e),     G = .gate [side, hidden], P = .proj [hidden, side]
 // and joins the stream through an RMS norm on its output (the sub-layer's output norm).  It reads the stream itself (no norm
-// in front).  forward_joined does the pending adds, the map, the norm and the add in one kernel; forward is the map alone.
+// in front).  The two maps are products over all tokens of the step (Linear: the decode product for a few tokens, the library
+// product above); forward_joined first takes in the outputs that are still to be added (one kernel: the adds and the rows the
+// product reads), and ends with the norm-and-add.
 // Parameters: hidden_size, vocab_size, side, column, columns, table (the table's tensor name).
 class TokenSide : public FeedForward {
 public:
@@ -251,7 +253,6 @@ public:
           column_((int)p.integer("column", 0)), columns_((int)p.integer("columns", p.integer("side"))), table_name_(p.text("table")) {
         if (hidden_ <= 0 || vocab_ <= 0 || side_ <= 0) throw std::invalid_argument("a token input's sizes must be positive");
         if (column_ < 0 || column_ + side_ > columns_) throw std::invalid_argument("a token input's columns lie outside its table");
-        if ((size_t)(hidden_ + side_) * 4 > 48 * 1024) throw std::invalid_argument("a token input takes hidden_size + side up to 12288");
     }
     std::vector<TensorRequest> tensor_requests() const override {
         return {TensorRequest::matrix(table_name_, vocab_, columns_), TensorRequest::matrix(prefix + ".gate", side_, hidden_),
@@ -263,33 +264,46 @@ public:
         std::vector<float> mine((size_t)vocab_ * side_);
         for (int v = 0; v < vocab_; ++v) std::memcpy(&mine[(size_t)v * side_], &all[(size_t)v * columns_ + column_], (size_t)side_ * 4);
         table_ = upload(mine.data(), mine.size(), dtype);
-        gate_ = upload(need_tensor(file, prefix + ".gate"), dtype);
-        proj_ = upload(need_tensor(file, prefix + ".proj"), dtype);
+        gate_ = Linear(need_tensor(file, prefix + ".gate"), nullptr, dtype);
+        proj_ = Linear(need_tensor(file, prefix + ".proj"), nullptr, dtype);
     }
-    size_t weight_bytes() const override { return (size_t)2 * side_ * hidden_ * 2; }
-    size_t arena_bytes(long long T) const override { return (size_t)T * hidden_ * 4 + (1u << 12); }
+    size_t weight_bytes() const override { return gate_.weight_bytes() + proj_.weight_bytes(); }
+    size_t arena_bytes(long long T) const override { return joined_arena_bytes(T); }
+    size_t joined_arena_bytes(long long T) const override { return (size_t)T * ((size_t)hidden_ * 8 + (size_t)side_ * 8) + (1u << 12); }
     bool capturable() const override { return true; }
 
     Delta forward(const StepContext& ctx, PartInput in, const FollowingNorm*) override {
         const Rows x = in.pending ? in.pending->materialize() : in.rows;
-        float* y = ctx.take<float>((size_t)ctx.num_tokens * hidden_);
-        launch_check(eg_token_side_rows(ctx.stream, (int)ctx.dtype, x.p, x.ld, y, ctx.token_ids, table_.get(), vocab_, gate_.get(), proj_.get(), ctx.num_tokens,
-                                        hidden_, side_, ctx.status), "token_side_rows");
+        const Rows y = map(ctx, x);
         Delta d;
-        d.p = y;
-        d.dtype = DType::F32;
+        d.p = y.p;
+        d.dtype = y.dtype;
         return d;
     }
     bool forward_joined(const StepContext& ctx, float* residual, const Delta& a, const Delta& b, const float* gain, float eps) override {
-        launch_check(eg_token_side(ctx.stream, (int)ctx.dtype, residual, a.p, (int)a.dtype, a.scale, b.p, (int)b.dtype, b.scale, ctx.token_ids, table_.get(), vocab_,
-                                   gate_.get(), proj_.get(), gain, eps, ctx.num_tokens, hidden_, side_, ctx.status), "token_side");
+        const int T = ctx.num_tokens;
+        Rows x{ctx.take_rows(T, hidden_, ctx.dtype), ctx.dtype, T, hidden_, hidden_};
+        launch_check(eg_add_scaled_rows(ctx.stream, residual, a.p, (int)a.dtype, a.scale, b.p, (int)b.dtype, b.scale, x.p, (int)x.dtype, T, hidden_), "add_scaled_rows");
+        const Rows y = map(ctx, x);
+        launch_check(eg_rmsnorm_add(ctx.stream, residual, y.p, (int)y.dtype, y.ld, gain, eps, T, hidden_), "rmsnorm_add");
         return true;
     }
 
 private:
+    // y float32 [T, hidden] = P (gelu_tanh(G x) * e)
+    Rows map(const StepContext& ctx, const Rows& x) const {
+        const int T = ctx.num_tokens;
+        const Rows z = gate_(ctx, x, /*out_f32=*/true);
+        Rows g{ctx.take_rows(T, side_, ctx.dtype), ctx.dtype, T, side_, side_};
+        launch_check(eg_token_side_gate(ctx.stream, (int)ctx.dtype, (const float*)z.p, z.ld, ctx.token_ids, table_.get(), vocab_, g.p, T, side_, ctx.status),
+                     "token_side_gate");
+        return proj_(ctx, g, /*out_f32=*/true);
+    }
+
     int hidden_, vocab_, side_, column_, columns_;
     std::string table_name_;
-    DeviceBuffer table_, gate_, proj_;
+    DeviceBuffer table_;
+    Linear gate_, proj_;
 };
 
 inline void register_mixed_parts() {
