@@ -33,23 +33,30 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// S[16 x 8 NKT] = Q[16 x wide] K^T: q_rows 16 rows of stride qs in shared memory, k_rows 8 NKT keys of stride ks
-template <int NKT>
-__device__ __forceinline__ void score_tile(float (&s)[NKT][4], const bf16* q_rows, int qs, const bf16* k_rows, int ks, int wide, int lane) {
+// S[16 MT x 8 NKT] = Q[16 MT x wide] K^T: q_rows 16 MT rows of stride qs in shared memory, k_rows 8 NKT keys of stride ks; a key
+// fragment serves the MT row tiles
+template <int MT, int NKT>
+__device__ __forceinline__ void score_tile(float (&s)[MT][NKT][4], const bf16* q_rows, int qs, const bf16* k_rows, int ks, int wide, int lane) {
 #pragma unroll
-    for (int i = 0; i < NKT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < NKT; ++i) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.f;
     const bf16* qa = q_rows + (lane & 15) * qs + (lane >> 4) * 8;
     const bf16* kb = k_rows + ((lane >> 4) * 8 + (lane & 7)) * ks + ((lane >> 3) & 1) * 8;
 #pragma unroll 2
     for (int k0 = 0; k0 < wide; k0 += 16) {
-        uint32_t a[4];
-        ldmatrix_x4(a, qa + k0);
+        uint32_t a[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(a[mt], qa + mt * 16 * qs + k0);
 #pragma unroll
         for (int np = 0; np < NKT / 2; ++np) {
             uint32_t b[4];
             ldmatrix_x4(b, kb + np * 16 * ks + k0);
-            mma_bf16_16816(s[2 * np], a, b[0], b[1]);
-            mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16_16816(s[mt][2 * np], a[mt], b[0], b[1]);
+                mma_bf16_16816(s[mt][2 * np + 1], a[mt], b[2], b[3]);
+            }
         }
     }
 }
@@ -91,17 +98,20 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NKT][4], float (&m)[2], 
     }
 }
 
-// O[16 x dk] += A[16 x 16] V[16 keys x dk]: v_rows 16 keys of stride vs, the head's first column already added
-template <int NT>
-__device__ __forceinline__ void value_step(float (&o)[NT][4], const uint32_t (&a)[4], const bf16* v_rows, int vs, int dk, int lane) {
+// O[16 MT x dk] += A[16 MT x 16] V[16 keys x dk]: v_rows 16 keys of stride vs, the head's first column already added
+template <int MT, int NT>
+__device__ __forceinline__ void value_step(float (&o)[MT][NT][4], const uint32_t (&a)[MT][4], const bf16* v_rows, int vs, int dk, int lane) {
     const bf16* vb = v_rows + (((lane >> 3) & 1) * 8 + (lane & 7)) * vs + (lane >> 4) * 8;
 #pragma unroll
     for (int dp = 0; dp < NT / 2; ++dp) {
         if (dp * 16 < dk) {
             uint32_t b[4];
             ldmatrix_x4_trans(b, vb + dp * 16);
-            mma_bf16_16816(o[2 * dp], a, b[0], b[1]);
-            mma_bf16_16816(o[2 * dp + 1], a, b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16_16816(o[mt][2 * dp], a[mt], b[0], b[1]);
+                mma_bf16_16816(o[mt][2 * dp + 1], a[mt], b[2], b[3]);
+            }
         }
     }
 }
@@ -124,18 +134,18 @@ struct TileParams {
 };
 
 // ---- prompt portions ---------------------------------------------------------------------------------------------------------
-template <int NT, int WARPS>
+template <int NT, int WARPS, int MT>
 __global__ void __launch_bounds__(WARPS * 32) mixed_tiles_kernel(const TileParams p) {
-    constexpr int TILE_ROWS = 16 * WARPS, SUBS = LISTED_ROWS / TILE_ROWS, NTHREADS = WARPS * 32;
+    constexpr int TILE_ROWS = 16 * MT * WARPS, SUBS = LISTED_ROWS / TILE_ROWS, NTHREADS = WARPS * 32;
     extern __shared__ __align__(16) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int dk = p.dk, wide = p.kv_heads * dk, qs = wide + 8, vs = dk + 8, cpr = wide / 8;
-    const int sub = p.num_subtiles - 1 - (int)blockIdx.x;       // the last tiles of a prompt have the most keys: they start first
+    const int sub = p.num_subtiles - 1 - (int)blockIdx.y;       // the last tiles of a prompt have the most keys: they start first, for all heads
     const int* tile = p.tiles + 3 * (sub / SUBS);
     const int first = tile[1] + TILE_ROWS * (sub % SUBS);
     const int count = min(TILE_ROWS, tile[2] - TILE_ROWS * (sub % SUBS));
     if (count <= 0) return;
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int c_own = h / (p.heads / p.kv_heads);
     const int* table = p.block_table + (size_t)tile[0] * p.table_stride;
 
@@ -182,14 +192,24 @@ __global__ void __launch_bounds__(WARPS * 32) mixed_tiles_kernel(const TileParam
     cp_async_commit();
     if (steps > 1) find_rows(1, 1);
 
-    const int row_lo = warp * 16 + (lane >> 2), row_hi = row_lo + 8;
-    const int limit_lo = row_lo < count ? p.positions[first + row_lo] : -1;
-    const int limit_hi = row_hi < count ? p.positions[first + row_hi] : -1;
-    const int warp_limit = warp * 16 < count ? p.positions[first + min(count - 1, warp * 16 + 15)] : -1;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[NT][4];
+    int limit[MT][2];
 #pragma unroll
-    for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (warp * MT + mt) * 16 + (lane >> 2) + 8 * r;
+            limit[mt][r] = row < count ? p.positions[first + row] : -1;
+        }
+    const int warp_limit = warp * MT * 16 < count ? p.positions[first + min(count - 1, warp * MT * 16 + MT * 16 - 1)] : -1;
+    float m[MT][2], l[MT][2];
+    float o[MT][NT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        m[mt][0] = m[mt][1] = -INFINITY;
+        l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < NT; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.f;
+    }
 
     for (int step = 0; step < steps; ++step) {
         const int buf = step & 1;
@@ -200,50 +220,62 @@ __global__ void __launch_bounds__(WARPS * 32) mixed_tiles_kernel(const TileParam
         if (step + 2 < steps) find_rows(step + 2, buf);
         const int key0 = step * BN;
         if (key0 > warp_limit) continue;
-        float s[BN / 8][4], corr[2];
-        score_tile<BN / 8>(s, q_s + warp * 16 * qs, qs, k_s + buf * BN * qs, qs, wide, lane);
-        softmax_tile<BN / 8>(s, m, l, corr, key0, limit_lo, limit_hi, lane);
+        float s[MT][BN / 8][4];
+        score_tile<MT, BN / 8>(s, q_s + warp * MT * 16 * qs, qs, k_s + buf * BN * qs, qs, wide, lane);
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-            o[i][0] *= corr[0];
-            o[i][1] *= corr[0];
-            o[i][2] *= corr[1];
-            o[i][3] *= corr[1];
+        for (int mt = 0; mt < MT; ++mt) {
+            float corr[2];
+            softmax_tile<BN / 8>(s[mt], m[mt], l[mt], corr, key0, limit[mt][0], limit[mt][1], lane);
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                o[mt][i][0] *= corr[0];
+                o[mt][i][1] *= corr[0];
+                o[mt][i][2] *= corr[1];
+                o[mt][i][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-            const uint32_t a[4] = {pack_bf16(s[2 * ks][0], s[2 * ks][1]), pack_bf16(s[2 * ks][2], s[2 * ks][3]), pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]),
-                                   pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3])};
-            value_step<NT>(o, a, v_s + (buf * BN + ks * 16) * vs, vs, dk, lane);
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                a[mt][0] = pack_bf16(s[mt][2 * ks][0], s[mt][2 * ks][1]);
+                a[mt][1] = pack_bf16(s[mt][2 * ks][2], s[mt][2 * ks][3]);
+                a[mt][2] = pack_bf16(s[mt][2 * ks + 1][0], s[mt][2 * ks + 1][1]);
+                a[mt][3] = pack_bf16(s[mt][2 * ks + 1][2], s[mt][2 * ks + 1][3]);
+            }
+            value_step<MT, NT>(o, a, v_s + (buf * BN + ks * 16) * vs, vs, dk, lane);
         }
     }
     cp_async_wait<0>();
 
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = r ? row_hi : row_lo;
-        if (row >= count) continue;
-        const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
-        const size_t t = (size_t)(first + row);
-        const float* g = p.gate ? p.gate + t * p.ld_gate + (size_t)h * dk : nullptr;
-        bf16* dst = p.out + t * p.ldo + (size_t)h * dk;
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int d = nt * 8 + 2 * (lane & 3);
-            if (d < dk) {
-                float a = o[nt][2 * r] * inv, b = o[nt][2 * r + 1] * inv;
-                if (g) {
-                    a *= sigmoid_f(g[d]);
-                    b *= sigmoid_f(g[d + 1]);
+        for (int r = 0; r < 2; ++r) {
+            const int row = (warp * MT + mt) * 16 + (lane >> 2) + 8 * r;
+            if (row >= count) continue;
+            const float inv = l[mt][r] > 0.f ? 1.0f / l[mt][r] : 0.f;
+            const size_t t = (size_t)(first + row);
+            const float* g = p.gate ? p.gate + t * p.ld_gate + (size_t)h * dk : nullptr;
+            bf16* dst = p.out + t * p.ldo + (size_t)h * dk;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int d = nt * 8 + 2 * (lane & 3);
+                if (d < dk) {
+                    float a = o[mt][nt][2 * r] * inv, b = o[mt][nt][2 * r + 1] * inv;
+                    if (g) {
+                        a *= sigmoid_f(g[d]);
+                        b *= sigmoid_f(g[d + 1]);
+                    }
+                    *(__nv_bfloat162*)(dst + d) = __floats2bfloat162_rn(a, b);
                 }
-                *(__nv_bfloat162*)(dst + d) = __floats2bfloat162_rn(a, b);
             }
         }
-    }
 }
 
-size_t tiles_smem(int wide, int dk, int warps) {
-    return (size_t)(16 * warps + 2 * BN) * (wide + 8) * 2 + (size_t)2 * BN * (dk + 8) * 2 + 2 * BN * 8 + (size_t)(wide / 8) * 4;
+size_t tiles_smem(int wide, int dk, int rows) {
+    return (size_t)(rows + 2 * BN) * (wide + 8) * 2 + (size_t)2 * BN * (dk + 8) * 2 + 2 * BN * 8 + (size_t)(wide / 8) * 4;
 }
 
 // ---- single tokens -----------------------------------------------------------------------------------------------------------
@@ -299,7 +331,8 @@ __global__ void __launch_bounds__(THREADS) mixed_split_kernel(const SplitParams 
     const int c_lo = (h0 + row_lo) / group, c_hi = (h0 + row_hi) / group;
     const int c_first = h0 / group, c_last = min(p.heads - 1, h0 + 15) / group;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[NT][4];
+    float o1[1][NT][4];
+    float(&o)[NT][4] = o1[0];
 #pragma unroll
     for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
@@ -325,8 +358,9 @@ __global__ void __launch_bounds__(THREADS) mixed_split_kernel(const SplitParams 
         cp_async_commit();
         cp_async_wait<0>();
         __syncwarp();
-        float s[2][4], corr[2];
-        score_tile<2>(s, q_s, qs, k_w, qs, wide, lane);
+        float s1[1][2][4], corr[2];
+        float(&s)[2][4] = s1[0];
+        score_tile<1, 2>(s1, q_s, qs, k_w, qs, wide, lane);
         softmax_tile<2>(s, m, l, corr, key0, k_end - 1, k_end - 1, lane);
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
@@ -337,8 +371,8 @@ __global__ void __launch_bounds__(THREADS) mixed_split_kernel(const SplitParams 
         }
         const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]), a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
         for (int c = c_first; c <= c_last; ++c) {              // the rows of value head c, the others' weights zero
-            const uint32_t a[4] = {c_lo == c ? a0 : 0u, c_hi == c ? a1 : 0u, c_lo == c ? a2 : 0u, c_hi == c ? a3 : 0u};
-            value_step<NT>(o, a, v_w + c * dk, qs, dk, lane);
+            const uint32_t a[1][4] = {{c_lo == c ? a0 : 0u, c_hi == c ? a1 : 0u, c_lo == c ? a2 : 0u, c_hi == c ? a3 : 0u}};
+            value_step<1, NT>(o1, a, v_w + c * dk, qs, dk, lane);
         }
     }
     __syncthreads();                                           // every warp is done with its slices: the space is used again
@@ -432,7 +466,7 @@ static int raise_smem(K kernel, size_t bytes) {
 EG_API int eg_mixed_attention_mma_takes(int heads, int kv_heads, int dk) {
     if (!sizes_taken(heads, kv_heads, dk)) return 0;
     const int wide = kv_heads * dk;
-    return tiles_smem(wide, dk, 4) <= (size_t)SMEM_LIMIT && split_smem(wide, padded_dk(dk)) <= (size_t)SMEM_LIMIT;
+    return tiles_smem(wide, dk, 64) <= (size_t)SMEM_LIMIT && split_smem(wide, padded_dk(dk)) <= (size_t)SMEM_LIMIT;
 }
 
 // q bfloat16 [tokens, heads, kv_heads * dk] (folded queries); tiles int32 [num_tiles, 3] = (entry, first token, count <= 128);
@@ -444,26 +478,29 @@ EG_API int eg_mixed_attention_tiles(cudaStream_t stream, const void* q, const vo
     if (!eg_mixed_attention_mma_takes(heads, kv_heads, dk)) return (int)cudaErrorInvalidValue;
     TileParams p{(const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, head_stride, page_stride, block_table, table_stride, positions, tiles, 2 * num_tiles,
                  gate, ld_gate, (bf16*)out, ldo, heads, kv_heads, dk, page_size, num_pages, status};
-    // eight warps (all 128 tokens of a listed tile) where their queries fit beside the keys, else four
-    const int warps = tiles_smem(kv_heads * dk, dk, 8) <= (size_t)SMEM_LIMIT ? 8 : 4;
-    const size_t smem = tiles_smem(kv_heads * dk, dk, warps);
-    const int subtiles = num_tiles * (LISTED_ROWS / (16 * warps));
+    // all 128 tokens of a listed tile in one CTA where their queries fit beside the keys (a warp holds 32 rows, so that a key
+    // fragment from shared memory serves two row tiles; heads of more than 128 values: 16 rows a warp), else 64 tokens
+    const int wide = kv_heads * dk;
+    const bool whole = tiles_smem(wide, dk, LISTED_ROWS) <= (size_t)SMEM_LIMIT;
+    const int rows = whole ? LISTED_ROWS : 64;
+    const size_t smem = tiles_smem(wide, dk, rows);
+    const int subtiles = num_tiles * (LISTED_ROWS / rows);
     p.num_subtiles = subtiles;
-    const dim3 grid(subtiles, heads);
+    const dim3 grid(heads, subtiles);
     int rc = 0;
-#define EG_MIXED_TILES(NT, W)                                                   \
-    do {                                                                        \
-        if ((rc = raise_smem(mixed_tiles_kernel<NT, W>, smem))) return rc;      \
-        mixed_tiles_kernel<NT, W><<<grid, W * 32, smem, stream>>>(p);           \
+#define EG_MIXED_TILES(NT, W, MT)                                                   \
+    do {                                                                            \
+        if ((rc = raise_smem(mixed_tiles_kernel<NT, W, MT>, smem))) return rc;      \
+        mixed_tiles_kernel<NT, W, MT><<<grid, W * 32, smem, stream>>>(p);           \
     } while (0)
-    if (warps == 8) {
-        if (dk <= 64) EG_MIXED_TILES(8, 8);
-        else if (dk <= 128) EG_MIXED_TILES(16, 8);
-        else EG_MIXED_TILES(32, 8);
+    if (whole) {
+        if (dk <= 64) EG_MIXED_TILES(8, 4, 2);
+        else if (dk <= 128) EG_MIXED_TILES(16, 4, 2);
+        else EG_MIXED_TILES(32, 8, 1);
     } else {
-        if (dk <= 64) EG_MIXED_TILES(8, 4);
-        else if (dk <= 128) EG_MIXED_TILES(16, 4);
-        else EG_MIXED_TILES(32, 4);
+        if (dk <= 64) EG_MIXED_TILES(8, 4, 1);
+        else if (dk <= 128) EG_MIXED_TILES(16, 4, 1);
+        else EG_MIXED_TILES(32, 4, 1);
     }
 #undef EG_MIXED_TILES
     return eg_launch_status();
