@@ -49,14 +49,14 @@ __device__ __forceinline__ void rows_inverse_rms(const float* first, long long s
 // NORMED: `rows` are h already; else they are the stream and h is computed here
 template <typename TO, bool NORMED>
 __global__ void conv_shift_kernel(const float* __restrict__ rows, const float* __restrict__ gain, float eps, const float* __restrict__ w,
-                                  const float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
+                                  float* __restrict__ state, long long slot_floats, const int* __restrict__ token_seq,
                                   const int* __restrict__ seq_starts, const int* __restrict__ seq_slots, TO* __restrict__ out, TO* __restrict__ plain_out,
-                                  int hidden, int taps) {
+                                  int hidden, int taps, int single) {
     __shared__ float scratch[MAX_TAPS][32];
     __shared__ float inv[MAX_TAPS];
     const int t = blockIdx.x, seq = token_seq[t], start = seq_starts[seq];
     const int back = min(taps - 1, t - start);                  // earlier rows that lie in this step
-    const float* slot = taps > 1 ? state + (size_t)seq_slots[seq] * slot_floats : nullptr;      // one tap: no earlier rows, no slot
+    float* slot = taps > 1 ? state + (size_t)seq_slots[seq] * slot_floats : nullptr;      // one tap: no earlier rows, no slot
     if (!NORMED) rows_inverse_rms(rows + (size_t)t * hidden, -(long long)hidden, back + 1, hidden, eps, scratch, inv);     // inv[d]: d rows back
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         const float g = NORMED ? 1.0f : gain[j];
@@ -77,6 +77,11 @@ __global__ void conv_shift_kernel(const float* __restrict__ rows, const float* _
         }
         out[(size_t)t * hidden + j] = from_f32<TO>(own + acc);
         if (plain_out) plain_out[(size_t)t * hidden + j] = from_f32<TO>(own);
+        if (single && taps > 1) {
+            // every entry of the step is one token: its block is the slot's only reader, so it moves the slot on itself
+            for (int r = 0; r + 2 < taps; ++r) slot[(size_t)r * hidden + j] = slot[(size_t)(r + 1) * hidden + j];
+            slot[(size_t)(taps - 2) * hidden + j] = own;
+        }
     }
 }
 
@@ -102,34 +107,36 @@ __global__ void conv_shift_state_kernel(const float* __restrict__ rows, const fl
 }
 
 template <bool NORMED>
-int launch_conv_shift(cudaStream_t stream, const float* rows, const float* gain, float eps, const float* w, const float* state, long long slot_floats,
+int launch_conv_shift(cudaStream_t stream, const float* rows, const float* gain, float eps, const float* w, float* state, long long slot_floats,
                       const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out, int out_dtype, int tokens, int hidden,
-                      int taps) {
+                      int taps, int single) {
     if (tokens <= 0) return 0;
     if (taps < 1 || taps > MAX_TAPS || hidden <= 0 || (taps > 1 && slot_floats < (long long)(taps - 1) * hidden)) return (int)cudaErrorInvalidValue;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (out_dtype == EG_BF16)
         conv_shift_kernel<bf16, NORMED><<<tokens, threads, 0, stream>>>(rows, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, (bf16*)out,
-                                                                       (bf16*)plain_out, hidden, taps);
+                                                                       (bf16*)plain_out, hidden, taps, single);
     else
         conv_shift_kernel<float, NORMED><<<tokens, threads, 0, stream>>>(rows, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, (float*)out,
-                                                                        (float*)plain_out, hidden, taps);
+                                                                        (float*)plain_out, hidden, taps, single);
     return eg_launch_status();
 }
 }  // namespace
 
 // stream float32 [tokens, hidden]; w float32 [hidden, taps] (the last tap weighs the token's own row); state float32
 // [slots, slot_floats] with this part's (taps - 1) * hidden values first; out and plain_out [tokens, hidden] in out_dtype
-EG_API int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, const float* state,
+// single != 0: every entry of the step is one token, and the slots move on here (no eg_conv_shift_state behind)
+EG_API int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, float* state,
                                  long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out,
-                                 int out_dtype, int tokens, int hidden, int taps) {
+                                 int out_dtype, int tokens, int hidden, int taps, int single) {
     return launch_conv_shift<false>(stream, residual, gain, eps, w, state, slot_floats, token_seq, seq_starts, seq_slots, out, plain_out, out_dtype, tokens, hidden,
-                                    taps);
+                                    taps, single);
 }
 
-EG_API int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, const float* state, long long slot_floats, const int* token_seq,
-                         const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps) {
-    return launch_conv_shift<true>(stream, rows, nullptr, 0.f, w, state, slot_floats, token_seq, seq_starts, seq_slots, out, nullptr, out_dtype, tokens, hidden, taps);
+EG_API int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, float* state, long long slot_floats, const int* token_seq,
+                         const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps, int single) {
+    return launch_conv_shift<true>(stream, rows, nullptr, 0.f, w, state, slot_floats, token_seq, seq_starts, seq_slots, out, nullptr, out_dtype, tokens, hidden, taps,
+                                   single);
 }
 
 // gain null: `rows` are normed already; else they are the stream and the slot receives gain * x / rms(x)

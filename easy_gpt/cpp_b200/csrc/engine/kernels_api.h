@@ -122,9 +122,9 @@ int eg_gated_delta_plan(int dk, int dv, int* rows_per_lane, int* lanes);
 // gated_delta.cu
 int eg_gated_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* aux, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps);
 // conv_shift.cu
-int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, const float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out, int out_dtype, int tokens, int hidden, int taps);
+int eg_rmsnorm_conv_shift(cudaStream_t stream, const float* residual, const float* gain, float eps, const float* w, float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, void* plain_out, int out_dtype, int tokens, int hidden, int taps, int single);
 // conv_shift.cu
-int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, const float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps);
+int eg_conv_shift(cudaStream_t stream, const float* rows, const float* w, float* state, long long slot_floats, const int* token_seq, const int* seq_starts, const int* seq_slots, void* out, int out_dtype, int tokens, int hidden, int taps, int single);
 // conv_shift.cu
 int eg_conv_shift_state(cudaStream_t stream, const float* rows, const float* gain, float eps, float* state, long long slot_floats, const int* seq_starts, const int* seq_slots, int num_seqs, int hidden, int taps);
 // attention_mixed.cu

@@ -48,18 +48,21 @@ public:
     size_t weight_bytes() const override { return (size_t)size_ * taps_ * 4; }
     bool capturable() const override { return true; }
     long long state_floats() const override { return (long long)(taps_ - 1) * size_; }
+    // a step of single tokens moves the slots on in the same kernel (a token's block is its slot's only reader)
     void forward(const StepContext& ctx, const float* rows, float* state, long long slot_floats, void* out, DType out_dtype) const override {
         launch_check(eg_conv_shift(ctx.stream, rows, w_.as<float>(), state, slot_floats, ctx.token_seq, ctx.seq_starts, ctx.seq_slots, out, (int)out_dtype,
-                                   ctx.num_tokens, size_, taps_), "conv_shift");
-        launch_check(eg_conv_shift_state(ctx.stream, rows, nullptr, 0.f, state, slot_floats, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, size_, taps_),
-                     "conv_shift_state");
+                                   ctx.num_tokens, size_, taps_, ctx.all_decode), "conv_shift");
+        if (!ctx.all_decode)
+            launch_check(eg_conv_shift_state(ctx.stream, rows, nullptr, 0.f, state, slot_floats, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, size_, taps_),
+                         "conv_shift_state");
     }
     bool forward_rms(const StepContext& ctx, const float* residual, const float* gain, float eps, float* state, long long slot_floats, void* out,
                      void* plain_out, DType out_dtype) const override {
         launch_check(eg_rmsnorm_conv_shift(ctx.stream, residual, gain, eps, w_.as<float>(), state, slot_floats, ctx.token_seq, ctx.seq_starts, ctx.seq_slots,
-                                           out, plain_out, (int)out_dtype, ctx.num_tokens, size_, taps_), "rmsnorm_conv_shift");
-        launch_check(eg_conv_shift_state(ctx.stream, residual, gain, eps, state, slot_floats, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, size_, taps_),
-                     "conv_shift_state");
+                                           out, plain_out, (int)out_dtype, ctx.num_tokens, size_, taps_, ctx.all_decode), "rmsnorm_conv_shift");
+        if (!ctx.all_decode)
+            launch_check(eg_conv_shift_state(ctx.stream, residual, gain, eps, state, slot_floats, ctx.seq_starts, ctx.seq_slots, ctx.num_seqs, size_, taps_),
+                         "conv_shift_state");
         return true;
     }
 

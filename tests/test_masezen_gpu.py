@@ -68,6 +68,11 @@ ALONE = {
     "attention_no_rotation": model([(attention(rot_dims=None), None)]),
     "attention_no_stretching": model([(attention(scaling=None), None)]),
     "attention_many_heads": model([(attention(heads=8, kv_heads=2, dim=64, scale=0.11, rot_dims=24, base=5e5, scaling=(6.0, 1024, 24.0, 2.0)), None)], width=128),
+    "attention_24_heads": model([(attention(heads=24, kv_heads=3, dim=16, scale=0.3, rot_dims=8), None)], width=96),
+    "attention_heads_of_48": model([(attention(heads=4, kv_heads=2, dim=48, scale=0.15, rot_dims=48, scaling=None), None)]),
+    "attention_wide_keys": model([(attention(heads=6, kv_heads=3, dim=256, scale=0.06, rot_dims=32), None)], width=96),
+    "attention_five_key_heads": model([(attention(heads=10, kv_heads=5, dim=128, scale=0.09, rot_dims=128, scaling=None), None)], width=96),
+    "attention_ten_key_heads": model([(attention(heads=10, kv_heads=10, dim=64, scale=0.12, rot_dims=16), None)], width=96),
     "attention_one_key_head": model([(attention(heads=4, kv_heads=1, dim=32, scale=0.2, rot_dims=32), None)]),
     "attention_large_heads": model([(attention(heads=2, kv_heads=2, dim=128, scale=0.09, rot_dims=64, scaling=None), None)], width=96),
     "attention_heads_of_256": model([(attention(heads=2, kv_heads=1, dim=256, scale=0.06, rot_dims=128, scaling=None), None)], width=96),
@@ -121,6 +126,26 @@ def test_each_mechanism_alone(folders, name, dtype):
     toks = tokens(cfg["vocab"], 75, 1)
     got = runner(folder, dtype).run([("a", toks, list(range(75)))])
     close(got, pm.forward(cfg, w, toks), dtype, name)
+
+
+@pytest.mark.parametrize("name", ["attention_many_heads", "attention_24_heads", "attention_heads_of_48", "attention_wide_keys", "attention_five_key_heads",
+                                  "attention_ten_key_heads", "attention_large_heads", "attention_heads_of_256", "attention_one_key_head"])
+def test_attention_sizes_in_portions_and_single_tokens(folders, name):
+    """Every form of the tensor-core attention kernels (heads of up to 64, 128 and 256 values, padded heads, one CTA or two a listed
+    tile, more than 16 heads): a prompt over two listed tiles, single tokens beside another request's portion, steps of short
+    entries only, and decoding, against the restatement of each request alone."""
+    folder, cfg, w = folders(name, ALONE[name], seed=3)
+    a, b = tokens(cfg["vocab"], 166, 5), tokens(cfg["vocab"], 150, 6)
+    want_a, want_b = pm.forward(cfg, w, a), pm.forward(cfg, w, b)
+    r = runner(folder, "bfloat16", pool_tokens=512)
+    close(r.run([("a", a[:150], list(range(150)))]), want_a[:150], "bfloat16", name + ": two tiles")
+    got = r.run([("a", a[150:151], [0]), ("b", b[:137], list(range(137)))])
+    close(got, np.concatenate([want_a[150:151], want_b[:137]]), "bfloat16", name + ": a token beside a portion")
+    got = r.run([("a", a[151:154], [0, 1, 2]), ("b", b[137:139], [0, 1])])
+    close(got, np.concatenate([want_a[151:154], want_b[137:139]]), "bfloat16", name + ": short entries")
+    for i in range(11):
+        got = r.run([("a", [a[154 + i]], [0]), ("b", [b[139 + i]], [0])])
+        close(got, np.stack([want_a[154 + i], want_b[139 + i]]), "bfloat16", name + f": decoding {i}")
 
 
 def test_the_restatements_own_pieces():
