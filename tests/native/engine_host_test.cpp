@@ -257,6 +257,64 @@ int main(int argc, char** argv) {
         CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "names stream addition 3"));
     }
 
+    // ---- a third listed design: one norm a layer read by two branches side by side, a convolution in front of the mixer, a token input behind --
+    {
+        const char* kSide = R"({"architecture": "Masezen", "vocab": 91, "width": 40, "norm": {"eps": 3e-6}, "canon": {"taps": 5}, "token_side": {"dim": 7},
+          "layers": [
+            {"type": "attention", "mixer": {"heads": 6, "kv_heads": 3, "dim": 16, "vdim": 16, "scale": 0.25,
+                                            "rot": {"base": 7000.0, "dims": 12, "scaling": {"factor": 2.0, "original": 128, "fast": 8.0, "slow": 2.0}}},
+             "mlp": {"kind": "dense", "ff": 56}},
+            {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 8, "scale": 0.5},
+             "mlp": {"kind": "moe", "router": {"experts": 5, "top": 3}, "expert": {"ff": 24, "limit": 2.5}, "shared": {"ff": 32, "limit": 1.25}}},
+            {"type": "attention", "mixer": {"heads": 4, "kv_heads": 4, "dim": 8, "scale": 0.3}, "mlp": null}]})";
+        const ModelSpec spec = ArchitectureRegistry::instance().build(json::parse(kSide));
+        CHECK(spec.architecture == "masezen" && spec.layers.size() == 3 && spec.vocab_size == 91 && spec.hidden_size == 40 && spec.run_order.size() == 3);
+        const LayerSpec& first = spec.layers[0];
+        CHECK(first.parallel && first.sublayers.size() == 3 && first.sequential_tail == 1);
+        const SubLayerSpec& mix = first.sublayers[0];
+        CHECK(mix.part.kind == "mixed_attention" && mix.part.prefix == "l0.mix" && mix.part.params.integer("heads") == 6 && mix.part.params.integer("kv_heads") == 3 &&
+              mix.part.params.integer("dim") == 16 && mix.part.params.real("scale") == 0.25 && mix.part.params.real("norm_eps") == 3e-6);
+        CHECK(mix.norm.kind == "rmsnorm" && mix.norm.prefix == "l0.norm1" && mix.norm.params.integer("single_gain") == 1 && mix.norm.params.real("eps") == 3e-6 &&
+              mix.output_norm.present && mix.output_norm.kind == "layer_scale" && mix.output_norm.prefix == "l0.ls1");
+        CHECK(mix.shift.present && mix.shift.kind == "conv_shift" && mix.shift.prefix == "l0.canon1" && mix.shift.params.integer("taps") == 5 &&
+              mix.shift.params.integer("size") == 40);
+        CHECK(first.position.present && first.position.params.integer("rotary_dim") == 12 && first.position.params.real("theta") == 7000.0 &&
+              first.position.params.real("scaling_factor") == 2.0 && first.position.params.real("scaling_original") == 128.0);
+        // the feed-forward has no norm of its own (it reads the mixer's), and a gain on its output
+        const SubLayerSpec& ff = first.sublayers[1];
+        CHECK(ff.part.kind == "squared_relu" && ff.part.prefix == "l0.mlp" && ff.part.params.integer("ff") == 56 && !ff.norm.present && !ff.shift.present &&
+              ff.output_norm.kind == "layer_scale" && ff.output_norm.prefix == "l0.ls2");
+        // every layer reads its own columns of the one table
+        const SubLayerSpec& side = spec.layers[1].sublayers[2];
+        CHECK(side.part.kind == "token_side" && side.part.prefix == "l1.side" && side.part.params.integer("side") == 7 && side.part.params.integer("column") == 7 &&
+              side.part.params.integer("columns") == 21 && side.part.params.text("table") == "side.embed" && !side.norm.present &&
+              side.output_norm.kind == "rmsnorm" && side.output_norm.prefix == "l1.side.norm");
+        const PartSpec& routed = spec.layers[1].sublayers[1].part;
+        CHECK(routed.kind == "routed_experts" && routed.params.integer("experts") == 5 && routed.params.integer("top") == 3 && routed.params.integer("ff") == 24 &&
+              routed.params.real("limit") == 2.5 && routed.params.integer("weight_input") == 1 && routed.params.integer("shared_ff") == 32 &&
+              routed.params.real("shared_limit") == 1.25 && routed.params.text("scoring") == "sigmoid");
+        // no rotation where the keys say nothing of one; a layer without a feed-forward has the mixer and the token input
+        CHECK(!spec.layers[1].position.present && spec.layers[2].sublayers.size() == 2 && spec.layers[2].sequential_tail == 1 &&
+              spec.layers[2].sublayers[0].part.kind == "mixed_attention" && spec.layers[2].sublayers[1].part.kind == "token_side");
+        auto changed = [&](const std::string& from, const std::string& to) {
+            std::string text = kSide;
+            const size_t at = text.find(from);
+            CHECK(at != std::string::npos);
+            text.replace(at, from.size(), to);
+            return text;
+        };
+        // neither a convolution nor a token input: the layers are the two branches alone
+        const ModelSpec bare = ArchitectureRegistry::instance().build(json::parse(changed(R"("canon": {"taps": 5}, "token_side": {"dim": 7},)", "")));
+        CHECK(bare.layers[0].sublayers.size() == 2 && bare.layers[0].sequential_tail == 0 && !bare.layers[0].sublayers[0].shift.present);
+        bool refused = false;
+        try {
+            ArchitectureRegistry::instance().build(json::parse(changed(R"("vdim": 16)", R"("vdim": 24)")));
+        } catch (const std::exception&) {
+            refused = true;
+        }
+        CHECK(refused);       // the values are the keys: another size for them is no model of this design
+    }
+
     // ---- a second listed design: branches normed on both sides, a shift in front of the mixer, a loop without additions -----------
     {
         const char* kListed = R"({"architecture": "Lasizen", "vocab": 83, "width": 48, "norm": {"eps": 2e-6}, "embedding": {"scale": 3.0},
