@@ -88,13 +88,15 @@ __global__ void squared_relu_kernel(const TI* __restrict__ x, long long ldx, TO*
     out[(size_t)t * ldo + c] = from_f32<TO>(z * z);
 }
 
+// bias: float32 [2 n], interleaved like the columns and added to them first; or null
 template <typename TI, typename TO>
-__global__ void clamped_glu_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int tokens, int n, float limit) {
+__global__ void clamped_glu_kernel(const TI* __restrict__ x, long long ldx, TO* __restrict__ out, long long ldo, int tokens, int n, float limit,
+                                   const float* __restrict__ bias) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)tokens * n) return;
     const int t = (int)(i / n), c = (int)(i % n);
-    const float g = fminf(to_f32<TI>(x[(size_t)t * ldx + 2 * c]), limit);
-    const float u = fminf(fmaxf(to_f32<TI>(x[(size_t)t * ldx + 2 * c + 1]), -limit), limit);
+    const float g = fminf(to_f32<TI>(x[(size_t)t * ldx + 2 * c]) + (bias ? bias[2 * c] : 0.f), limit);
+    const float u = fminf(fmaxf(to_f32<TI>(x[(size_t)t * ldx + 2 * c + 1]) + (bias ? bias[2 * c + 1] : 0.f), -limit), limit);
     out[(size_t)t * ldo + c] = from_f32<TO>(g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
 }
 
@@ -109,14 +111,20 @@ EG_API int eg_squared_relu(cudaStream_t stream, const void* x, int x_dtype, long
     return eg_launch_status();
 }
 
-// x [tokens, 2 n] interleaved -> out [tokens, n]
-EG_API int eg_clamped_glu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float limit) {
+// x [tokens, 2 n] interleaved -> out [tokens, n]; bias float32 [2 n] (interleaved alike, added to x first) or null
+EG_API int eg_clamped_glu_bias(cudaStream_t stream, const void* x, int x_dtype, long long ldx, const float* bias, void* out, int out_dtype, long long ldo, int tokens,
+                               int n, float limit) {
     const long long total = (long long)tokens * n;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (x_dtype == EG_F32 && out_dtype == EG_F32) clamped_glu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (float*)out, ldo, tokens, n, limit);
-    else if (x_dtype == EG_F32) clamped_glu_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (bf16*)out, ldo, tokens, n, limit);
-    else if (out_dtype == EG_F32) clamped_glu_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (float*)out, ldo, tokens, n, limit);
-    else clamped_glu_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (bf16*)out, ldo, tokens, n, limit);
+    if (x_dtype == EG_F32 && out_dtype == EG_F32) clamped_glu_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (float*)out, ldo, tokens, n, limit, bias);
+    else if (x_dtype == EG_F32) clamped_glu_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)x, ldx, (bf16*)out, ldo, tokens, n, limit, bias);
+    else if (out_dtype == EG_F32) clamped_glu_kernel<bf16, float><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (float*)out, ldo, tokens, n, limit, bias);
+    else clamped_glu_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, ldx, (bf16*)out, ldo, tokens, n, limit, bias);
     return eg_launch_status();
+}
+
+// x [tokens, 2 n] interleaved -> out [tokens, n]
+EG_API int eg_clamped_glu(cudaStream_t stream, const void* x, int x_dtype, long long ldx, void* out, int out_dtype, long long ldo, int tokens, int n, float limit) {
+    return eg_clamped_glu_bias(stream, x, x_dtype, ldx, nullptr, out, out_dtype, ldo, tokens, n, limit);
 }

@@ -550,6 +550,158 @@ inline ModelSpec masezen_spec(const json::Value& config) {
     return spec;
 }
 
+// ---- Mozalix ---------------------------------------------------------------------------------------------------------------
+// A decoder whose config.json lists its layers one by one.  A layer's branches read the stream itself and are normed on their
+// way back into it, x = x + n1(mixer(x)), x = x + n2(ff(x)), with RMS norms whose gains are stored around zero (1 + w).  The
+// mixer is one of three: "attention" (grouped heads, q and k normed per head with a shared gain and then turned, keys of the
+// query's own block of mask.size positions, a learned sink per head), "attention_2" (two softmax maps a head over a sliding
+// window, the second taken off the first with one weight for the layer, the difference normed per head) and "parallel" (an
+// attention without positions, with unit-rms q and k, capped scores and a window that also keeps the sequence's first tokens,
+// beside a gated delta-rule mixer with a decay per key channel; the two outputs are summed with a weight each).  The
+// feed-forward is a gated one with clamped gate and up values and biases on all three maps, or none.  A layer with
+// "weights_of": j runs layer j's tensors on a cache and state of its own.  The embedding is scaled by embedding.scale.  Every
+// size and constant is a key of config.json; tensor names are "l<i>.<part>.<tensor>".
+inline ModelSpec mozalix_spec(const json::Value& config) {
+    using C = GufanexConfig;        // the typed readers (a key's path goes into the refusal)
+    if (!config.is_object()) throw ConfigError("config.json is not a JSON object");
+    ModelSpec spec;
+    spec.architecture = "mozalix";
+    const long long width = C::integer(config, "width", ""), vocab = C::integer(config, "vocab", "");
+    if (width <= 0 || vocab <= 0) throw ConfigError("width and vocab must be > 0");
+    const double eps = C::number(C::need(config, "norm", ""), "eps", "norm.");
+    if (eps <= 0.0) throw ConfigError("norm.eps must be > 0");
+    spec.vocab_size = vocab;
+    spec.hidden_size = width;
+    spec.max_positions = C::integer_or(config, "max_positions", 1LL << 30, "");     // the design sets no limit; positions are 32-bit
+    auto norm = [&](const std::string& name) {
+        return PartSpec{"rmsnorm", Params{{"size", width}, {"eps", eps}, {"weight_name", ""}, {"offset", 1.0}}, name, true};
+    };
+    // the sizes every attention of this design has, and its mask's size if it has a mask
+    auto attention = [&](const json::Value& m, const std::string& w, long long* mask_size) {
+        const long long heads = C::integer(m, "heads", w), kv_heads = C::integer(m, "kv_heads", w), dim = C::integer(m, "dim", w), vdim = C::integer(m, "vdim", w);
+        if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || heads % kv_heads)
+            throw ConfigError(w + "heads, kv_heads, dim and vdim must be > 0, heads a multiple of kv_heads");
+        *mask_size = 0;
+        if (C::present(m, "mask")) {
+            *mask_size = C::integer(*m.find("mask"), "size", w + "mask.");
+            if (*mask_size <= 0) throw ConfigError(w + "mask.size must be > 0");
+        }
+        return Params{{"hidden_size", width}, {"heads", heads}, {"kv_heads", kv_heads}, {"dim", dim}, {"vdim", vdim}, {"scale", C::number(m, "scale", w)},
+                      {"norm_eps", eps}};
+    };
+    auto rotation = [&](const json::Value& m, const std::string& w) {
+        if (!C::present(m, "rot")) return PartSpec::none();
+        const json::Value& rot = *m.find("rot");
+        const long long dims = C::integer(rot, "dims", w + "rot."), dim = C::integer(m, "dim", w);
+        if (dims < 0 || dims % 2 || dims > dim) throw ConfigError(w + "rot.dims must be even and within dim");
+        if (dims == 0) return PartSpec::none();
+        return PartSpec{"rope", Params{{"head_dim", dim}, {"rotary_dim", dims}, {"theta", C::number(rot, "base", w + "rot.")}}, "", true};
+    };
+    const json::Value& layers = C::need(config, "layers", "");
+    if (!layers.is_array() || layers.array.empty()) throw ConfigError("layers must be a list with at least one layer");
+    const long long count = (long long)layers.array.size();
+    // whose tensors a layer uses: its own, or (through "weights_of", possibly in several steps) another layer's
+    std::vector<long long> owner(count);
+    for (long long i = 0; i < count; ++i) {
+        long long j = i;
+        for (long long hops = 0; C::present(layers.array[j], "weights_of"); ++hops) {
+            const std::string where = "layers[" + std::to_string(j) + "].";
+            j = C::integer(layers.array[j], "weights_of", where);
+            if (j < 0 || j >= count || hops > count) throw ConfigError(where + "weights_of must name a layer that has tensors of its own");
+        }
+        owner[i] = j;
+    }
+    std::vector<int> built(count, -1);           // layer index -> index into spec.layers, for layers with tensors of their own
+    for (long long i = 0; i < count; ++i) {
+        if (owner[i] != i) continue;
+        const json::Value& l = layers.array[i];
+        const std::string where = "layers[" + std::to_string(i) + "].", prefix = "l" + std::to_string(i), w = where + "mixer.";
+        const json::Value& type = C::need(l, "type", where);
+        const json::Value& m = C::need(l, "mixer", where);
+        if (!type.is_string()) throw ConfigError(where + "type must be a string");
+        LayerSpec layer;
+        PartSpec mixer;
+        long long mask = 0;
+        if (type.string == "attention") {
+            Params a = attention(m, w, &mask);
+            a.set("qk_norm", "gain");
+            a.set("sinks", 1);
+            if (mask > 0) a.set("chunk", mask);
+            mixer = PartSpec{"masked_attention", a, prefix + ".mix", true};
+            layer.position = rotation(m, w);
+        } else if (type.string == "attention_2") {
+            Params a = attention(m, w, &mask);
+            a.set("qk_norm", "gain");
+            a.set("maps", 2);
+            a.set("diff", C::number(m, "diff", w));
+            if (mask > 0) a.set("window", mask);
+            mixer = PartSpec{"masked_attention", a, prefix + ".mix", true};
+            layer.position = rotation(m, w);
+        } else if (type.string == "parallel") {
+            const json::Value& left = C::need(m, "left", w);
+            const json::Value& right = C::need(m, "right", w);
+            const std::string wl = w + "left.", wr = w + "right.";
+            Params a = attention(left, wl, &mask);
+            a.set("qk_norm", "unit");
+            if (mask > 0) {
+                a.set("window", mask);
+                const long long keep = C::integer_or(*left.find("mask"), "keep_first", 0, wl + "mask.");
+                if (keep < 0) throw ConfigError(wl + "mask.keep_first must not be negative");
+                a.set("keep_first", keep);
+            }
+            if (C::present(left, "softcap")) {
+                const double cap = C::number(left, "softcap", wl);
+                if (cap <= 0.0) throw ConfigError(wl + "softcap must be > 0");
+                a.set("softcap", cap);
+            }
+            a.set("out_scale", C::number(m, "left_scale", w));
+            const long long heads = C::integer(right, "heads", wr), kv_heads = C::integer(right, "kv_heads", wr), dim = C::integer(right, "dim", wr),
+                            vdim = C::integer(right, "vdim", wr), conv = C::integer(right, "conv", wr);
+            if (heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || heads % kv_heads || conv < 1)
+                throw ConfigError(wr + "heads, kv_heads, dim, vdim and conv must be > 0, heads a multiple of kv_heads");
+            Params d{{"hidden_size", width}, {"heads", heads}, {"kv_heads", kv_heads}, {"dim", dim}, {"vdim", vdim}, {"conv", conv}, {"eps", eps}, {"unit_eps", 1e-6},
+                     {"gate", "sigmoid"}, {"out_scale", C::number(m, "right_scale", w)}};
+            if (C::present(right, "rank")) d.set("rank", C::integer(right, "rank", wr));        // only what random-weights mode writes: a file's tensors decide
+            Params both{{"left_kind", "masked_attention"}, {"right_kind", "channel_delta"}};
+            both.merge("left.", a);
+            both.merge("right.", d);
+            mixer = PartSpec{"side_by_side", both, prefix + ".mix", true};
+        } else {
+            throw ConfigError(where + "type '" + type.string + "' is no mixer of this design (attention, attention_2, parallel)");
+        }
+        layer.sublayers.push_back({"mixer", mixer, PartSpec::none(), "pre", norm(prefix + ".norm1")});
+        if (C::present(l, "mlp")) {
+            const json::Value& mlp = *l.find("mlp");
+            const std::string wm = where + "mlp.";
+            const json::Value& kind = C::need(mlp, "kind", wm);
+            if (!kind.is_string() || kind.string != "dense") throw ConfigError(wm + "kind must be 'dense'");
+            const long long ff = C::integer(mlp, "ff", wm);
+            const double limit = C::number(mlp, "limit", wm);
+            if (ff <= 0 || limit <= 0.0) throw ConfigError(wm + "ff and limit must be > 0");
+            Params f{{"hidden_size", width}, {"intermediate_size", ff}, {"bias", true}, {"activation", "clamped"}, {"limit", limit}, {"gate_name", ".gate"},
+                     {"up_name", ".up"}, {"down_name", ".down"}, {"gate_bias_name", ".gate.b"}, {"up_bias_name", ".up.b"}, {"down_bias_name", ".down.b"}};
+            layer.sublayers.push_back({"feed_forward", PartSpec{"swiglu", f, prefix + ".mlp", true}, PartSpec::none(), "pre", norm(prefix + ".norm2")});
+        }
+        built[i] = (int)spec.layers.size();
+        spec.layers.push_back(std::move(layer));
+    }
+    for (long long i = 0; i < count; ++i) {
+        const json::Value& l = layers.array[i];
+        if (owner[i] != i) {
+            const json::Value &mine = C::need(l, "type", "layers[" + std::to_string(i) + "]."), &theirs = C::need(layers.array[owner[i]], "type", "");
+            if (!mine.is_string() || mine.string != theirs.string)
+                throw ConfigError("layers[" + std::to_string(i) + "] uses the tensors of a layer of another type");
+        }
+        spec.run_order.push_back(RunEntry{built[owner[i]], (int)i, true});
+    }
+    Params embedding{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}};
+    if (C::present(config, "embedding")) embedding.set("scale", C::number(*config.find("embedding"), "scale", "embedding."));
+    spec.embedding = PartSpec{"embedding", embedding, "embed", true};
+    spec.final_norm = norm("final.norm");
+    spec.lm_head = PartSpec{"lm_head", Params{{"vocab_size", vocab}, {"hidden_size", width}, {"weight_name", ""}}, "head", true};
+    return spec;
+}
+
 inline void register_builtin_architectures() {
     ArchitectureRegistry& r = ArchitectureRegistry::instance();
     for (auto& e : r.entries)
@@ -558,6 +710,7 @@ inline void register_builtin_architectures() {
     r.add("gufanex", gufanex_spec);
     r.add("lasizen", lasizen_spec);
     r.add("masezen", masezen_spec);
+    r.add("mozalix", mozalix_spec);
 }
 
 }  // namespace easygpt::engine

@@ -157,4 +157,22 @@ int eg_gemm_tcgen05_pair_relu2(cudaStream_t stream, const void* A, long long lda
 int eg_gemm_tcgen05_pair_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int M, int N, int K, int* status, float limit);
 // gemm_tcgen05.cu
 int eg_gemm_tcgen05_grouped_glu(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, void* out, long long ldo, int max_rows, int N, int K, int groups, const int* tile_group, int* status, float limit);
+// attention_masked.cu
+int eg_masked_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude, const int* slot_map, void* k_cache, void* v_cache, int row_stride, long long head_stride, int page_size, long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int maps, int dk, int dv, float norm_eps, const float* q_gain, const float* k_gain, int* status);
+// attention_masked.cu
+int eg_masked_attention(cudaStream_t stream, int dtype, const void* q, const void* k_cache, const void* v_cache, int row_stride, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out, int out_dtype, long long ldo, int num_tokens, int heads, int kv_heads, int maps, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale, int* status);
+// attention_masked.cu
+int eg_attention_map_difference(cudaStream_t stream, const float* maps, void* out, int out_dtype, long long ldo, int tokens, int heads, int dv, float lambda, float eps, float post);
+// gated_delta.cu
+int eg_gated_delta_channel(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* b, long long ldb, int b_col, float* decay, long long ldg, const float* z, long long ldz, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y, int y_dtype, long long ldy, float* aux, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps, int gate_sigmoid, float out_scale);
+// engine_ops.cu
+int eg_add_bias_rows(cudaStream_t stream, float* x, long long ld, const float* bias, int rows, int cols);
+// engine_ops.cu
+int eg_convert_columns(cudaStream_t stream, const float* src, long long lds, void* dst, int dst_dtype, long long ldd, int rows, int cols, int padded);
+// activation.cu
+int eg_clamped_glu_bias(cudaStream_t stream, const void* x, int x_dtype, long long ldx, const float* bias, void* out, int out_dtype, long long ldo, int tokens, int n, float limit);
+// gemm_skinny.cu
+int eg_gemm_skinny_clamped_glu_bias(cudaStream_t stream, int use_pdl, const void* W, long long ldw, const float* bias, int M, int N, int K, const void* x, long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status, float limit);
+// gemm_tcgen05.cu
+int eg_gemm_tcgen05_pair_glu_bias(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out, long long ldo, int M, int N, int K, int* status, float limit);
 }  // extern "C"

@@ -8,6 +8,7 @@
 #include "architectures.hpp"
 #include "parts.hpp"
 #include "parts_delta.hpp"
+#include "parts_masked.hpp"
 #include "parts_mixed.hpp"
 #include "parts_sequence.hpp"
 
@@ -324,6 +325,7 @@ public:
         register_sequence_parts();
         register_delta_parts();
         register_mixed_parts();
+        register_masked_parts();
         spec.validate();
         PartRegistry& reg = PartRegistry::instance();
         embedding = PartRegistry::find(reg.embeddings, "embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding.prefix);

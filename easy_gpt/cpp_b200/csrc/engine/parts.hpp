@@ -172,8 +172,8 @@ public:
         const int cols = limit > 0.f ? N / 2 : N;
         Rows out{ctx.take_rows(M, cols, DType::BF16), DType::BF16, M, cols, cols};
         if (limit > 0.f)
-            launch_check(eg_gemm_skinny_clamped_glu(ctx.stream, plans::use_pdl(), weight, in_features, M, N, in_features, x.p, x.ld, out.p, cols, plan.row_blocks,
-                                                    plan.k_slices, plan.k_split, partials, counters, ctx.status, limit), "gemm_skinny_clamped_glu");
+            launch_check(eg_gemm_skinny_clamped_glu_bias(ctx.stream, plans::use_pdl(), weight, in_features, bias_f32(), M, N, in_features, x.p, x.ld, out.p, cols,
+                                                         plan.row_blocks, plan.k_slices, plan.k_split, partials, counters, ctx.status, limit), "gemm_skinny_clamped_glu");
         else
             launch_check(eg_gemm_skinny_relu2(ctx.stream, plans::use_pdl(), weight, in_features, M, N, in_features, x.p, x.ld, out.p, N, plan.row_blocks,
                                               plan.k_slices, plan.k_split, partials, counters, ctx.status), "gemm_skinny_relu2");
@@ -209,12 +209,24 @@ public:
             skinny(ctx, out_f32 ? plans::EPI_F32 : plans::EPI_STORE, M, &x, nullptr, out.p, out_features, nullptr, nullptr, nullptr, nullptr, nullptr);
             return out;
         }
-        if (out_f32 && has_bias()) throw DeviceError("a library product into float32 takes no bias");
-        ctx.blas->gemm_bf16(ctx.stream, x.p, x.ld, weight, in_features, has_bias() ? bias_lp_.get() : nullptr, out.p, out_features, M, out_features,
+        // the library's product into float32 takes no bias: it is added by a kernel behind it, in float32
+        ctx.blas->gemm_bf16(ctx.stream, x.p, x.ld, weight, in_features, has_bias() && !out_f32 ? bias_lp_.get() : nullptr, out.p, out_features, M, out_features,
                             in_features, out_f32);
+        if (out_f32 && has_bias()) launch_check(eg_add_bias_rows(ctx.stream, (float*)out.p, out_features, bias_f32(), M, out_features), "add_bias_rows");
         return out;
     }
 
+    // the bare product into float32, for a consumer whose own kernel adds the bias
+    Rows without_bias_f32(const StepContext& ctx, const Rows& x) const {
+        const int M = x.rows;
+        Rows out{ctx.take_rows(M, out_features, DType::F32), DType::F32, M, out_features, out_features};
+        if (dtype == DType::F32)
+            launch_check(eg_gemm_f32_nt(ctx.stream, (const float*)x.p, (int)x.ld, (const float*)weight, in_features, nullptr, (float*)out.p, out_features, M,
+                                        out_features, in_features), "gemm_f32_nt");
+        else
+            ctx.blas->gemm_bf16(ctx.stream, x.p, x.ld, weight, in_features, nullptr, out.p, out_features, M, out_features, in_features, true);
+        return out;
+    }
     const float* bias_f32() const { return bias_f32_.get() ? bias_f32_.as<float>() : nullptr; }
     bool has_bias() const { return bias_f32_.get() != nullptr; }
 
@@ -238,13 +250,15 @@ class RMSNorm : public Norm {
 public:
     RMSNorm(const Params& p, const std::string& prefix)
         : Norm(p, prefix), size_((int)p.integer("size")), eps_((float)p.real("eps")), weight_name_(prefix + p.text("weight_name", ".weight")),
-          single_(p.integer("single_gain", 0) != 0) {}
+          single_(p.integer("single_gain", 0) != 0), offset_((float)p.real("offset", 0.0)) {}
     std::vector<TensorRequest> tensor_requests() const override {
-        return {(single_ ? TensorRequest::scalar(weight_name_) : TensorRequest::vector(weight_name_, size_)).with_init("one")};
+        return {(single_ ? TensorRequest::scalar(weight_name_) : TensorRequest::vector(weight_name_, size_)).with_init(offset_ != 0.f ? "zero" : "one")};
     }
     void load(const HostTensors& file, DType) override {
         std::vector<float> g = host_floats(need_tensor(file, weight_name_));       // gains are used in float32 whatever they were stored in
         if (single_) g.assign((size_t)size_, g.at(0));                               // one number for all coordinates: the kernels read a gain per channel
+        if (offset_ != 0.f)                                                          // a gain stored around zero: the kernels read offset + w
+            for (float& v : g) v += offset_;
         gain_ = upload(g.data(), g.size(), DType::F32);
     }
     size_t weight_bytes() const override { return (size_t)size_ * 4; }
@@ -280,6 +294,7 @@ private:
     float eps_;
     std::string weight_name_;      // parameter weight_name: the gain's tensor name as a suffix of the prefix (default ".weight")
     bool single_;                  // parameter single_gain: the tensor is ONE number, the gain of every coordinate
+    float offset_;                 // parameter offset: the gain is offset + the stored tensor (1 for a gain stored around zero)
     DeviceBuffer gain_;
 };
 
@@ -673,8 +688,9 @@ public:
     SwiGLU(const Params& p, const std::string& prefix)
         : FeedForward(p, prefix), hidden_((int)p.integer("hidden_size")), inter_((int)p.integer("intermediate_size")), bias_(p.flag("bias", false)),
           gate_name_(prefix + p.text("gate_name", ".gate_proj.weight")), up_name_(prefix + p.text("up_name", ".up_proj.weight")),
-          down_name_(prefix + p.text("down_name", ".down_proj.weight")), clamped_(p.text("activation", "swiglu") == "clamped"),
-          limit_((float)p.real("limit", 0.0)) {
+          down_name_(prefix + p.text("down_name", ".down_proj.weight")), gate_bias_name_(prefix + p.text("gate_bias_name", ".gate_proj.bias")),
+          up_bias_name_(prefix + p.text("up_bias_name", ".up_proj.bias")), down_bias_name_(prefix + p.text("down_bias_name", ".down_proj.bias")),
+          clamped_(p.text("activation", "swiglu") == "clamped"), limit_((float)p.real("limit", 0.0)) {
         if (p.text("activation", "swiglu") != "swiglu" && !clamped_) throw std::invalid_argument("a gated feed-forward's activation is 'swiglu' or 'clamped'");
         if (clamped_ && !(limit_ > 0.f)) throw std::invalid_argument("a clamped gate needs a positive limit");
     }
@@ -682,9 +698,9 @@ public:
         std::vector<TensorRequest> r = {TensorRequest::matrix(gate_name_, inter_, hidden_), TensorRequest::matrix(up_name_, inter_, hidden_),
                                         TensorRequest::matrix(down_name_, hidden_, inter_)};
         if (bias_) {
-            r.push_back(TensorRequest::vector(prefix + ".gate_proj.bias", inter_));
-            r.push_back(TensorRequest::vector(prefix + ".up_proj.bias", inter_));
-            r.push_back(TensorRequest::vector(prefix + ".down_proj.bias", hidden_));
+            r.push_back(TensorRequest::vector(gate_bias_name_, inter_).with_init("zero"));
+            r.push_back(TensorRequest::vector(up_bias_name_, inter_).with_init("zero"));
+            r.push_back(TensorRequest::vector(down_bias_name_, hidden_).with_init("zero"));
         }
         return r;
     }
@@ -697,10 +713,10 @@ public:
         }
         std::vector<float> db;
         if (bias_) {
-            const std::vector<float> gb = host_floats(need_tensor(file, prefix + ".gate_proj.bias")), ub = host_floats(need_tensor(file, prefix + ".up_proj.bias"));
+            const std::vector<float> gb = host_floats(need_tensor(file, gate_bias_name_)), ub = host_floats(need_tensor(file, up_bias_name_));
             b.resize((size_t)2 * inter_);
             for (int i = 0; i < inter_; ++i) { b[2 * i] = gb[i]; b[2 * i + 1] = ub[i]; }
-            db = host_floats(need_tensor(file, prefix + ".down_proj.bias"));
+            db = host_floats(need_tensor(file, down_bias_name_));
         }
         gate_up_ = Linear(w.data(), 2 * inter_, hidden_, bias_ ? b.data() : nullptr, dtype);
         down_ = Linear(need_tensor(file, down_name_), bias_ ? db.data() : nullptr, dtype);
@@ -750,11 +766,13 @@ public:
             if (plans::gemm_skinny_takes(dtype, T, hidden_) && Linear::aligned(x)) {
                 act = gate_up_.skinny_clamped_glu(ctx, x, limit_);
             } else if (plans::gemm_tcgen05_wide_takes(dtype, T, 2 * inter_, hidden_) && Linear::aligned(x)) {
-                launch_check(eg_gemm_tcgen05_pair_glu(ctx.stream, x.p, x.ld, gate_up_.weight, hidden_, act.p, inter_, T, 2 * inter_, hidden_, ctx.status, limit_),
-                             "gemm_tcgen05_pair_glu");
+                launch_check(eg_gemm_tcgen05_pair_glu_bias(ctx.stream, x.p, x.ld, gate_up_.weight, hidden_, gate_up_.bias_f32(), act.p, inter_, T, 2 * inter_,
+                                                           hidden_, ctx.status, limit_), "gemm_tcgen05_pair_glu");
             } else {
-                const Rows gu = gate_up_(ctx, x, /*out_f32=*/true);
-                launch_check(eg_clamped_glu(ctx.stream, gu.p, (int)gu.dtype, gu.ld, act.p, (int)dtype, inter_, T, inter_, limit_), "clamped_glu");
+                // the bare product in float32; biases, limits and the gate in one kernel behind it
+                const Rows gu = gate_up_.without_bias_f32(ctx, x);
+                launch_check(eg_clamped_glu_bias(ctx.stream, gu.p, (int)gu.dtype, gu.ld, gate_up_.bias_f32(), act.p, (int)dtype, inter_, T, inter_, limit_),
+                             "clamped_glu");
             }
             const Rows o = down_(ctx, act, /*out_f32=*/true);
             Delta d;
@@ -794,6 +812,7 @@ private:
     int hidden_, inter_;
     bool bias_;
     std::string gate_name_, up_name_, down_name_;      // the weights' tensor names (parameters gate_name / up_name / down_name: suffixes of the prefix)
+    std::string gate_bias_name_, up_bias_name_, down_bias_name_;    // with bias: the biases' names (parameters *_bias_name, suffixes alike)
     bool clamped_;                                     // parameter activation "clamped" (with limit) instead of "swiglu"
     float limit_;
     Linear gate_up_, down_;

@@ -37,13 +37,17 @@ struct CacheNeed {
     int num_kv_heads = 0, head_dim = 0;
     int planes = 2;                         // PagedKV: 2 = keys and values; 1 = one row per token (a latent that serves as both)
     long long window = -1;                  // PagedKV: < 0 keeps all keys
-    std::vector<long long> state_shape;     // State: a tensor of this shape per live request, zeroed when a request starts
+    long long keep_first = 0;               // PagedKV with a window: the first positions of a request stay for good beside the window
+    // State: a tensor of this shape per live request, zeroed when a request starts.  A PagedKV need may name one too (a
+    // mixer of two halves, one with cached keys and one with a recurrent state): it then gets pages AND a slot.
+    std::vector<long long> state_shape;
     DType state_dtype = DType::F32;
     // float32 values per live request that the layer's own parts keep beside the mixer (a shift's last row), whatever
     // the mixer's kind; zeroed when a request starts.  Set by the model, not by the mixer.
     long long layer_state_floats = 0;
     bool same_pages(const CacheNeed& o) const {
-        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && planes == o.planes && window == o.window;
+        return kind == o.kind && num_kv_heads == o.num_kv_heads && head_dim == o.head_dim && planes == o.planes && window == o.window &&
+               keep_first == o.keep_first;
     }
     bool operator==(const CacheNeed& o) const {
         return same_pages(o) && state_shape == o.state_shape && state_dtype == o.state_dtype && layer_state_floats == o.layer_state_floats;
@@ -66,6 +70,19 @@ struct CacheNeed {
     static CacheNeed paged_joint(int kv_heads, int key_dim, int value_dim, long long window) {
         CacheNeed n = paged(kv_heads, key_dim + value_dim, window);
         n.planes = 1;
+        return n;
+    }
+    // the same need with a per-request tensor beside its pages
+    CacheNeed with_state(std::vector<long long> shape, DType dtype = DType::F32) const {
+        CacheNeed n = *this;
+        n.state_shape = std::move(shape);
+        n.state_dtype = dtype;
+        return n;
+    }
+    // the first `count` positions stay beside the window
+    CacheNeed keeping_first(long long count) const {
+        CacheNeed n = *this;
+        n.keep_first = window < 0 ? 0 : count;
         return n;
     }
     static CacheNeed state(std::vector<long long> shape, DType dtype = DType::F32) {

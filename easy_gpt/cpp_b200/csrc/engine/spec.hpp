@@ -63,6 +63,18 @@ public:
         return p.s;
     }
 
+    // the parameters whose keys start with `head`, with the head taken off: the parameters of a part inside a part
+    Params sub(const std::string& head) const {
+        Params out;
+        for (auto& kv : map_)
+            if (kv.first.size() > head.size() && kv.first.compare(0, head.size(), head) == 0) out.map_[kv.first.substr(head.size())] = kv.second;
+        return out;
+    }
+    // all of `other` under keys that start with `head`
+    void merge(const std::string& head, const Params& other) {
+        for (auto& kv : other.map_) map_[head + kv.first] = kv.second;
+    }
+
 private:
     const Param& need(const std::string& key) const {
         auto it = map_.find(key);

@@ -75,7 +75,7 @@ public:
                 if (!g) {
                     groups.emplace_back(new Group());
                     g = groups.back().get();
-                    g->index = core.add_group(num_pages, need.window < 0 ? -1 : (int)need.window);
+                    g->index = core.add_group(num_pages, need.window < 0 ? -1 : (int)need.window, (int)need.keep_first);
                     g->need = need;
                     g->num_pages = num_pages;
                     g->scratch_page = num_pages;
@@ -83,7 +83,8 @@ public:
                 }
                 g->cache_ids.push_back(kv.first);
                 group_of_cache[kv.first] = g->index;
-            } else if (need.kind == CacheNeed::State) {
+            }
+            if (need.kind == CacheNeed::State || (need.kind == CacheNeed::PagedKV && !need.state_shape.empty())) {
                 size_t elems = 1;
                 for (long long s : need.state_shape) elems *= (size_t)s;
                 State st;
@@ -124,7 +125,6 @@ public:
             v.head_stride = (long long)page_size * g.need.head_dim;
             v.num_pages = g.num_pages + 1;
             v.page_size = page_size;
-            return v;
         }
         auto st = states.find(cache_id);
         if (st != states.end()) {

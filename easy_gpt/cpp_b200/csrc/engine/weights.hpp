@@ -189,6 +189,27 @@ struct TensorRequest {
     // what random-weights mode draws for it: "" a normal value, "one" / "zero" / "half" a constant, "log_decay" the logarithm of a
     // decay rate between 1 and 16, "step_bias" the inverse softplus of a step size between 1e-3 and 1e-1
     std::string init;
+    // dimensions whose extent the file decides (a low-rank pair's inner size): the request's own extent there is only what
+    // random-weights mode writes
+    std::vector<int> free_dims;
+    TensorRequest with_free_dim(int dim) const {
+        TensorRequest r = *this;
+        r.free_dims.push_back(dim);
+        return r;
+    }
+    bool fits(const std::vector<long long>& stored) const {
+        for (auto& want : shapes) {
+            if (want == stored) return true;
+            if (free_dims.empty() || want.size() != stored.size()) continue;
+            bool ok = true;
+            for (size_t d = 0; d < want.size(); ++d) {
+                const bool is_free = std::find(free_dims.begin(), free_dims.end(), (int)d) != free_dims.end();
+                if (is_free ? stored[d] <= 0 : stored[d] != want[d]) ok = false;
+            }
+            if (ok) return true;
+        }
+        return false;
+    }
     TensorRequest with_init(const char* how) const {
         TensorRequest r = *this;
         r.init = how;
@@ -220,9 +241,10 @@ inline void check_manifest(const std::vector<TensorRequest>& requests, const Saf
             if (!r.optional) missing.push_back(r.name);
             continue;
         }
-        if (!r.shapes.empty() && std::find(r.shapes.begin(), r.shapes.end(), t->shape) == r.shapes.end()) {
+        if (!r.shapes.empty() && !r.fits(t->shape)) {
             std::string expected;
             for (size_t i = 0; i < r.shapes.size(); ++i) expected += (i ? " or " : "") + shape_list(r.shapes[i]);
+            for (int d : r.free_dims) expected += " (dimension " + std::to_string(d) + " free)";
             wrong.push_back("Invalid tensor shape for key '" + r.name + "': expected " + expected + ", got " + shape_list(t->shape));
         }
     }

@@ -66,3 +66,40 @@ EG_API int eg_softcap(cudaStream_t stream, float* x, long long n, float cap) {
     softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, n, cap, 1.0f / cap);
     return eg_launch_status();
 }
+
+namespace {
+__global__ void add_bias_rows_kernel(float* __restrict__ x, long long ld, const float* __restrict__ bias, int rows, int cols) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * cols) return;
+    const int c = (int)(i % cols);
+    x[(size_t)(i / cols) * ld + c] += bias[c];
+}
+template <typename TD>
+__global__ void convert_columns_kernel(const float* __restrict__ src, long long lds, TD* __restrict__ dst, long long ldd, int rows, int cols, int padded) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * padded) return;
+    const int c = (int)(i % padded);
+    const size_t r = (size_t)(i / padded);
+    dst[r * ldd + c] = from_f32<TD>(c < cols ? src[r * lds + c] : 0.f);
+}
+}  // namespace
+
+// x [rows, ld] float32: x[r, c] += bias[c], c < cols (the bias of a product whose library form writes float32 without one)
+EG_API int eg_add_bias_rows(cudaStream_t stream, float* x, long long ld, const float* bias, int rows, int cols) {
+    const long long n = (long long)rows * cols;
+    if (n <= 0) return 0;
+    add_bias_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, ld, bias, rows, cols);
+    return eg_launch_status();
+}
+
+// A block of columns of float32 rows as rows of their own: dst[r, c] = src[r, c] for c < cols and 0 for cols <= c < padded
+// (dst_dtype EG_F32 or EG_BF16; rows lds and ldd elements apart).  For a product that reads a few columns of another's output.
+EG_API int eg_convert_columns(cudaStream_t stream, const float* src, long long lds, void* dst, int dst_dtype, long long ldd, int rows, int cols, int padded) {
+    const long long n = (long long)rows * padded;
+    if (n <= 0) return 0;
+    if (padded < cols) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dst_dtype == EG_BF16) convert_columns_kernel<bf16><<<blocks, 256, 0, stream>>>(src, lds, (bf16*)dst, ldd, rows, cols, padded);
+    else convert_columns_kernel<float><<<blocks, 256, 0, stream>>>(src, lds, (float*)dst, ldd, rows, cols, padded);
+    return eg_launch_status();
+}

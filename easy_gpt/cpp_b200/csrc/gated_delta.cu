@@ -17,6 +17,12 @@
 // shared memory by asynchronous copies, the next tile's behind this one's steps; outputs are normed per head and gated by
 // the block itself where it holds whole heads, else by a kernel behind.  The slot keeps S as [head, dv, dk], so that a
 // thread's rows are neighbours in memory.  The order of every sum depends on the sizes alone.
+//
+// A second form has a decay per head AND key channel, g [dk]: S <- diag(g) S (the rows of S decay each at its own rate), the
+// rest as above.  With S' = diag(g) S_old:  u = beta (v - S'^T k^),  o = S'^T q^ + u (k^ . q^), so a token costs the same two
+// dot products, over the decayed rows; the tile's decays are staged beside its keys and queries.  Its per-token numbers come
+// from buffers of their own (beta's logits, the decays' step-size logits, the output gate), the gate is a sigmoid or a silu,
+// and the output may carry a factor.
 #include <algorithm>
 #include <cstdlib>
 
@@ -95,22 +101,67 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* __restrict__ 
     }
 }
 
+// The same for the form with a decay per key channel: unit vectors and k^ . q^ per key head, beta per head, and the decays
+// g = exp(-exp(A_log[head]) * softplus(a + dt_bias)) written over their logits a in `decay` [tokens, ldg] (heads x dk, dt_bias alike).
+__global__ void __launch_bounds__(128) delta_prepare_channel_kernel(float* __restrict__ qkv, long long ldq, int q_col, int k_col, const float* __restrict__ b,
+                                                                    long long ldb, int b_col, float* __restrict__ decay, long long ldg,
+                                                                    const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                                                    float* __restrict__ aux, int tokens, int heads, int kv_heads, int dk, float unit_eps) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= (long long)tokens * kv_heads) return;
+    const int t = (int)(w / kv_heads), g = (int)(w % kv_heads);
+    float* q = qkv + (size_t)t * ldq + q_col + (size_t)g * dk;
+    float* k = qkv + (size_t)t * ldq + k_col + (size_t)g * dk;
+    float kk = 0.f, qq = 0.f, kq = 0.f;
+    for (int d = lane; d < dk; d += 32) {
+        const float a = k[d], c = q[d];
+        kk = fmaf(a, a, kk);
+        qq = fmaf(c, c, qq);
+        kq = fmaf(a, c, kq);
+    }
+    kk = warp_sum(kk);
+    qq = warp_sum(qq);
+    kq = warp_sum(kq);
+    const float ik = 1.0f / sqrtf(kk + unit_eps), iq = (1.0f / sqrtf((float)dk)) / sqrtf(qq + unit_eps);
+    for (int d = lane; d < dk; d += 32) {
+        k[d] *= ik;
+        q[d] *= iq;
+    }
+    const int per = heads / kv_heads;
+    for (int i = 0; i < per; ++i) {
+        const int head = g * per + i;
+        const float rate = -expf(a_log[head]);
+        float* row = decay + (size_t)t * ldg + (size_t)head * dk;
+        for (int d = lane; d < dk; d += 32) row[d] = decay_exp(rate * softplus_f(row[d] + dt_bias[(size_t)head * dk + d]));
+        if (lane == 0) {
+            float* out = aux + ((size_t)t * heads + head) * 4;
+            out[0] = 1.0f / (1.0f + expf(-b[(size_t)t * ldb + b_col + head]));
+            out[1] = 1.0f;
+            out[2] = kq * ik * iq;
+            out[3] = 0.f;
+        }
+    }
+}
+
 // grid (heads, entries, column slices): a block holds `cols` columns of a head's S.  With o_raw the block leaves its columns
 // of o there (float32) and the norm over the head's columns is another kernel's; without, the block holds whole heads and
 // norms and gates its outputs itself.  The tiles' keys, queries, values and (beta, g, k . q) come by asynchronous copies into
 // one of two buffers, the next tile's while this one's steps run.
-template <typename TO, int R, int P>
+// CH: the form with a decay per key channel (`decay` [tokens, ldg], heads x dk), staged beside keys and queries.
+template <typename TO, int R, int P, bool CH>
 __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restrict__ qkv, long long ldq, int q_col, int k_col, int v_col,
                                                            const float* __restrict__ proj, long long ldp, int z_col, const float* __restrict__ aux,
                                                            const float* __restrict__ norm_w, float* __restrict__ state, long long slot_floats,
                                                            long long state_offset, const int* __restrict__ seq_starts,
                                                            const int* __restrict__ seq_slots, TO* __restrict__ y, long long ldy,
                                                            float* __restrict__ o_raw, int cols, int heads, int kv_heads, int dk, int dv, float eps,
-                                                           int wide) {
+                                                           int wide, const float* __restrict__ decay, long long ldg, int gate_sigmoid, float out_scale) {
     extern __shared__ __align__(16) float smem[];
     constexpr int RS = R + PAD, DKS = RS * P;       // a part's stride, a staged row's length (rows beyond dk hold zeros)
+    constexpr int VECS = CH ? 3 : 2;                // staged vectors of dk values a token: key, query and, with CH, decay
     const int vcols = (cols + 3) & ~3;
-    const int stage_floats = TILE * (2 * DKS + vcols + 4);
+    const int stage_floats = TILE * (VECS * DKS + vcols + 4);
     float* s_o = smem + 2 * stage_floats;           // [TILE, cols]
     const int head = blockIdx.x, seq = blockIdx.y, j0 = blockIdx.z * cols;
     const int kvh = head / (heads / kv_heads);
@@ -133,7 +184,8 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
         const int t0 = ti * TILE, n = min(TILE, count - t0);
         float* sk = smem + b * stage_floats;
         float* sq = sk + TILE * DKS;
-        float* sv = sq + TILE * DKS;
+        float* sg = sq + TILE * DKS;                // with CH only
+        float* sv = sk + VECS * TILE * DKS;
         float* sa = sv + TILE * vcols;
         if (wide) {
             const int pieces = dk / 4;
@@ -143,6 +195,7 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
                 const int at = t * DKS + (d / R) * RS + d % R;
                 copy_async_16(sk + at, row + k_col + kvh * dk + d);
                 copy_async_16(sq + at, row + q_col + kvh * dk + d);
+                if (CH) copy_async_16(sg + at, decay + (size_t)(start + t0 + t) * ldg + (size_t)head * dk + d);
             }
             const int vp = width / 4;
             for (int i = threadIdx.x; i < n * vp; i += blockDim.x) {
@@ -157,6 +210,7 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
                 const int at = t * DKS + (d / R) * RS + d % R;
                 copy_async_4(sk + at, row + k_col + kvh * dk + d);
                 copy_async_4(sq + at, row + q_col + kvh * dk + d);
+                if (CH) copy_async_4(sg + at, decay + (size_t)(start + t0 + t) * ldg + (size_t)head * dk + d);
             }
             for (int i = threadIdx.x; i < n * width; i += blockDim.x) {
                 const int t = i / width, d = i % width;
@@ -180,13 +234,22 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
         __syncthreads();                            // this tile has arrived; the tile before is done with s_o
         const float* s_k = smem + (ti & 1) * stage_floats;
         const float* s_q = s_k + TILE * DKS;
-        const float* s_v = s_q + TILE * DKS;
+        const float* s_g = s_q + TILE * DKS;        // with CH only
+        const float* s_v = s_k + VECS * TILE * DKS;
         const float* s_a = s_v + TILE * vcols;
         auto step = [&](int t) {
             const float4* kt = reinterpret_cast<const float4*>(s_k + t * DKS + part * RS);
             const float4* qt = reinterpret_cast<const float4*>(s_q + t * DKS + part * RS);
             float kv[R];
             float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;
+            if (CH) {                                   // the rows decay first, each at its own rate; the sums run over the decayed rows
+                const float4* gt = reinterpret_cast<const float4*>(s_g + t * DKS + part * RS);
+#pragma unroll
+                for (int r = 0; r < R; r += 4) {
+                    const float4 c = gt[r / 4];
+                    s[r] *= c.x; s[r + 1] *= c.y; s[r + 2] *= c.z; s[r + 3] *= c.w;
+                }
+            }
 #pragma unroll
             for (int r = 0; r < R; r += 4) {
                 const float4 a = kt[r / 4], b = qt[r / 4];
@@ -201,7 +264,7 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
             }
             const float4 bgk = *reinterpret_cast<const float4*>(s_a + t * 4);      // beta, g, k . q
-            const float g = bgk.y;
+            const float g = CH ? 1.0f : bgk.y;
             const float u = bgk.x * ((active ? s_v[t * vcols + jl] : 0.f) - g * sk);
 #pragma unroll
             for (int r = 0; r < R; ++r) s[r] = fmaf(kv[r], u, g * s[r]);
@@ -229,7 +292,8 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
             const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
             const float* z = proj + (size_t)(start + t0 + t) * ldp + z_col + head * dv;
             TO* out = y + (size_t)(start + t0 + t) * ldy + head * dv;
-            for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(s_o[t * cols + d] * inv * norm_w[d] * silu_f(z[d]));
+            for (int d = lane; d < dv; d += 32)
+                out[d] = from_f32<TO>(s_o[t * cols + d] * inv * norm_w[d] * (gate_sigmoid ? 1.0f / (1.0f + expf(-z[d])) : silu_f(z[d])) * out_scale);
         }
     }
     if (active) {
@@ -244,7 +308,8 @@ __global__ void __launch_bounds__(1024) gated_delta_kernel(const float* __restri
 // y = o / rms(o) * w * silu(z) per (token, head), a warp each: behind a recurrence whose blocks held slices of a head
 template <typename TO>
 __global__ void delta_output_kernel(const float* __restrict__ o_raw, const float* __restrict__ proj, long long ldp, int z_col,
-                                    const float* __restrict__ norm_w, TO* __restrict__ y, long long ldy, int tokens, int heads, int dv, float eps) {
+                                    const float* __restrict__ norm_w, TO* __restrict__ y, long long ldy, int tokens, int heads, int dv, float eps,
+                                    int gate_sigmoid, float out_scale) {
     const int lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (w >= (long long)tokens * heads) return;
@@ -256,14 +321,24 @@ __global__ void delta_output_kernel(const float* __restrict__ o_raw, const float
     const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     const float* z = proj + (size_t)t * ldp + z_col + head * dv;
     TO* out = y + (size_t)t * ldy + head * dv;
-    for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(o[d] * inv * norm_w[d] * silu_f(z[d]));
+    for (int d = lane; d < dv; d += 32) out[d] = from_f32<TO>(o[d] * inv * norm_w[d] * (gate_sigmoid ? 1.0f / (1.0f + expf(-z[d])) : silu_f(z[d])) * out_scale);
 }
 
-template <typename TO, int R, int P>
+// what the form with a decay per key channel brings beside the common arguments (decay null: the form with one decay a head)
+struct ChannelForm {
+    const float* b = nullptr;       // beta's logits [tokens, ldb], head h at b_col + h
+    long long ldb = 0;
+    float* decay = nullptr;         // [tokens, ldg], heads x dk: the decays' logits on entry, the decays after the preparation
+    long long ldg = 0;
+    int gate_sigmoid = 0;           // the output gate is sigmoid(z) instead of silu(z)
+    float out_scale = 1.0f;
+};
+
+template <typename TO, int R, int P, bool CH>
 int launch_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp, int b_col,
                  int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
                  long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* aux, float* o_raw, int slices,
-                 int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+                 int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps, const ChannelForm& cf) {
     // columns per block: whole warps of them (32 / P columns a warp), and a multiple of four so that the slices' values start on 16-byte boundaries
     const int per_warp = 32 / P < 4 ? 4 : 32 / P;
     const int most_cols = 1024 / P / per_warp * per_warp;       // a block has at most 1024 threads
@@ -275,25 +350,30 @@ int launch_delta(cudaStream_t stream, float* qkv, long long ldq, int q_col, int 
     if (slices == 1) o_raw = nullptr;
     const int threads = cols * P;
     const int vcols = (cols + 3) & ~3;
-    const size_t smem = ((size_t)2 * TILE * (2 * (R + PAD) * P + vcols + 4) + (size_t)TILE * cols) * sizeof(float);
+    const size_t smem = ((size_t)2 * TILE * ((CH ? 3 : 2) * (R + PAD) * P + vcols + 4) + (size_t)TILE * cols) * sizeof(float);
     if (threads > 1024 || smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    auto kernel = gated_delta_kernel<TO, R, P>;
+    auto kernel = gated_delta_kernel<TO, R, P, CH>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     const long long prep = (long long)tokens * kv_heads;
-    delta_prepare_kernel<<<(unsigned)((prep + 3) / 4), 128, 0, stream>>>(qkv, ldq, q_col, k_col, proj, ldp, b_col, a_col, a_log, dt_bias, aux, tokens, heads,
-                                                                         kv_heads, dk, unit_eps);
+    if (CH)
+        delta_prepare_channel_kernel<<<(unsigned)((prep + 3) / 4), 128, 0, stream>>>(qkv, ldq, q_col, k_col, cf.b, cf.ldb, b_col, cf.decay, cf.ldg, a_log, dt_bias,
+                                                                                     aux, tokens, heads, kv_heads, dk, unit_eps);
+    else
+        delta_prepare_kernel<<<(unsigned)((prep + 3) / 4), 128, 0, stream>>>(qkv, ldq, q_col, k_col, proj, ldp, b_col, a_col, a_log, dt_bias, aux, tokens, heads,
+                                                                             kv_heads, dk, unit_eps);
     // 16-byte copies need every copied row to start on a 16-byte boundary
     const int wide = dk % 4 == 0 && dv % 4 == 0 && ldq % 4 == 0 && q_col % 4 == 0 && k_col % 4 == 0 && v_col % 4 == 0 && (uintptr_t)qkv % 16 == 0 &&
-                     (uintptr_t)aux % 16 == 0;
+                     (uintptr_t)aux % 16 == 0 && (!CH || (cf.ldg % 4 == 0 && (uintptr_t)cf.decay % 16 == 0));
     kernel<<<dim3(heads, num_seqs, slices), threads, smem, stream>>>(qkv, ldq, q_col, k_col, v_col, proj, ldp, z_col, aux, norm_w, state, slot_floats,
                                                                      state_offset, seq_starts, seq_slots, (TO*)y, ldy, o_raw, cols, heads, kv_heads, dk, dv,
-                                                                     eps, wide);
+                                                                     eps, wide, cf.decay, cf.ldg, cf.gate_sigmoid, cf.out_scale);
     if (o_raw) {
         const long long warps = (long long)tokens * heads;
-        delta_output_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(o_raw, proj, ldp, z_col, norm_w, (TO*)y, ldy, tokens, heads, dv, eps);
+        delta_output_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(o_raw, proj, ldp, z_col, norm_w, (TO*)y, ldy, tokens, heads, dv, eps,
+                                                                                 cf.gate_sigmoid, cf.out_scale);
     }
     return eg_launch_status();
 }
@@ -302,12 +382,15 @@ template <typename TO>
 int dispatch_delta(int R, int P, cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* proj, long long ldp,
                    int b_col, int a_col, int z_col, const float* a_log, const float* dt_bias, const float* norm_w, float* state, long long slot_floats,
                    long long state_offset, const int* seq_starts, const int* seq_slots, void* y, long long ldy, float* aux, float* o_raw, int slices,
-                   int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps) {
+                   int tokens, int num_seqs, int heads, int kv_heads, int dk, int dv, float unit_eps, float eps, const ChannelForm& cf = ChannelForm()) {
 #define EG_DELTA(RR, PP)                                                                                                                                  \
     if (R == RR && P == PP)                                                                                                                               \
-        return launch_delta<TO, RR, PP>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats, \
-                                        state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, \
-                                        eps)
+        return cf.decay ? launch_delta<TO, RR, PP, true>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state,  \
+                                                         slot_floats, state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads,  \
+                                                         kv_heads, dk, dv, unit_eps, eps, cf)                                                                     \
+                        : launch_delta<TO, RR, PP, false>(stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, \
+                                                          slot_floats, state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, \
+                                                          kv_heads, dk, dv, unit_eps, eps, cf)
     EG_DELTA(4, 4);
     EG_DELTA(8, 4);
     EG_DELTA(8, 8);
@@ -354,4 +437,30 @@ EG_API int eg_gated_delta(cudaStream_t stream, float* qkv, long long ldq, int q_
                                     state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
     return dispatch_delta<float>(R, P, stream, qkv, ldq, q_col, k_col, v_col, proj, ldp, b_col, a_col, z_col, a_log, dt_bias, norm_w, state, slot_floats,
                                  state_offset, seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps);
+}
+
+// The form with a decay per head and key channel.  qkv, aux, state, y, o_raw and slices as above.  b float32 [tokens, ldb] holds
+// beta's logits (head h at b_col + h); decay float32 [tokens, ldg] holds, heads x dk, the logits a of the decays on entry and
+// the decays g = exp(-exp(A_log[head]) softplus(a + dt_bias)) afterwards (dt_bias [heads x dk]); z float32 [tokens, ldz] the
+// output gate's logits (heads x dv); the gate is sigmoid(z) (gate_sigmoid) or silu(z); y carries the factor out_scale.
+EG_API int eg_gated_delta_channel(cudaStream_t stream, float* qkv, long long ldq, int q_col, int k_col, int v_col, const float* b, long long ldb, int b_col,
+                                  float* decay, long long ldg, const float* z, long long ldz, const float* a_log, const float* dt_bias, const float* norm_w,
+                                  float* state, long long slot_floats, long long state_offset, const int* seq_starts, const int* seq_slots, void* y,
+                                  int y_dtype, long long ldy, float* aux, float* o_raw, int slices, int tokens, int num_seqs, int heads, int kv_heads, int dk,
+                                  int dv, float unit_eps, float eps, int gate_sigmoid, float out_scale) {
+    if (num_seqs <= 0 || tokens <= 0) return 0;
+    int R = 0, P = 0;
+    if (kv_heads <= 0 || heads % kv_heads || !eg_gated_delta_plan(dk, dv, &R, &P) || slices < 1 || !aux || !decay || !b || !z) return (int)cudaErrorInvalidValue;
+    ChannelForm cf;
+    cf.b = b;
+    cf.ldb = ldb;
+    cf.decay = decay;
+    cf.ldg = ldg;
+    cf.gate_sigmoid = gate_sigmoid;
+    cf.out_scale = out_scale;
+    if (y_dtype == EG_BF16)
+        return dispatch_delta<bf16>(R, P, stream, qkv, ldq, q_col, k_col, v_col, z, ldz, b_col, 0, 0, a_log, dt_bias, norm_w, state, slot_floats, state_offset,
+                                    seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps, cf);
+    return dispatch_delta<float>(R, P, stream, qkv, ldq, q_col, k_col, v_col, z, ldz, b_col, 0, 0, a_log, dt_bias, norm_w, state, slot_floats, state_offset,
+                                 seq_starts, seq_slots, y, ldy, aux, o_raw, slices, tokens, num_seqs, heads, kv_heads, dk, dv, unit_eps, eps, cf);
 }

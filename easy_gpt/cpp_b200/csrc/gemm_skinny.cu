@@ -779,3 +779,12 @@ EG_API int eg_gemm_skinny_clamped_glu(cudaStream_t stream, int use_pdl, const vo
                            k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
                            nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 3, limit, 0.f);
 }
+
+// The same with a bias float32 [N] (interleaved like the rows of W) added to the finished sums in front of the gate.
+EG_API int eg_gemm_skinny_clamped_glu_bias(cudaStream_t stream, int use_pdl, const void* W, long long ldw, const float* bias, int M, int N, int K, const void* x,
+                                           long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters,
+                                           int* status, float limit) {
+    return gemm_skinny_any(stream, EPI_SWIGLU, 0, use_pdl, W, ldw, bias, M, N, K, x, ldx, nullptr, nullptr, nullptr, nullptr, 0.f, out, ldo, row_blocks,
+                           k_slices, k_split, scratch, counters, 0, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, status, nullptr, 0,
+                           nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr, 3, limit, 0.f);
+}

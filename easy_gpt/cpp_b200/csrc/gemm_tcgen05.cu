@@ -1158,3 +1158,10 @@ EG_API int eg_gemm_tcgen05_pair_glu(cudaStream_t stream, const void* A, long lon
     if (!(limit > 0.f)) return (int)cudaErrorInvalidValue;
     return gemm_tcgen05_pair_any(stream, EPI_SWIGLU, A, lda, W, ldw, nullptr, out, ldo, M, N, K, 256, status, nullptr, limit, 0.f);
 }
+
+// The same with a bias float32 [N] (interleaved like the rows of W) added to the sums in front of the gate.
+EG_API int eg_gemm_tcgen05_pair_glu_bias(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out,
+                                         long long ldo, int M, int N, int K, int* status, float limit) {
+    if (!(limit > 0.f)) return (int)cudaErrorInvalidValue;
+    return gemm_tcgen05_pair_any(stream, EPI_SWIGLU, A, lda, W, ldw, bias, out, ldo, M, N, K, 256, status, nullptr, limit, 0.f);
+}

@@ -1,7 +1,9 @@
 // Bookkeeping of the paged cache: one page pool and one block table per group of caches with the
 // same needs, request slots, and per request the tokens committed and reserved.  A group that keeps
 // all keys holds ceil(length / page_size) pages per request; a group with a window gives a page back
-// as soon as every position in it has left the window of all tokens still to come.  Host code only:
+// as soon as every position in it has left the window of all tokens still to come; a windowed group
+// may also keep the first positions of every request for good (keys that stay visible whatever the
+// distance), and then never gives back the pages that hold them.  Host code only:
 // device memory belongs to the caller, which addresses it with the page ids kept here.
 //
 // (The reference has no pages: its per-sample caches grow by concatenation,
@@ -22,8 +24,10 @@ namespace easygpt::host {
 struct CacheGroup {
     PagePool pool;
     int window;                         // < 0: all keys are kept
+    int keep_first;                     // with a window: positions 0 .. keep_first - 1 of a request stay for good
     std::vector<int32_t> tables;        // [max_slots][max_pages_per_request], -1 where no page is held
-    CacheGroup(int num_pages, int window_, size_t table_ints) : pool(num_pages), window(window_), tables(table_ints, -1) {}
+    CacheGroup(int num_pages, int window_, int keep_first_, size_t table_ints)
+        : pool(num_pages), window(window_), keep_first(keep_first_ > 0 ? keep_first_ : 0), tables(table_ints, -1) {}
 };
 
 struct CachedRequest {
@@ -41,8 +45,8 @@ public:
         slot_is_fresh_.assign(max_slots, 0);
     }
 
-    int add_group(int num_pages, int window) {
-        groups_.emplace_back(new CacheGroup(num_pages, window, (size_t)max_slots_ * max_pages_));
+    int add_group(int num_pages, int window, int keep_first = 0) {
+        groups_.emplace_back(new CacheGroup(num_pages, window, keep_first, (size_t)max_slots_ * max_pages_));
         for (auto& kv : requests_) kv.second.first_live_page.push_back(0);
         return (int)groups_.size() - 1;
     }
@@ -177,7 +181,9 @@ public:
             CacheGroup& grp = *groups_[g];
             if (grp.window < 0) continue;
             const long long first_key = r.length - grp.window + 1 > 0 ? r.length - grp.window + 1 : 0;
-            const int first = (int)(first_key / page_size_), old = r.first_live_page[g];
+            // the pages that hold kept first positions are never given back: the release starts behind them
+            const int kept = (int)ceil_div(grp.keep_first, page_size_);
+            const int first = (int)(first_key / page_size_), old = r.first_live_page[g] > kept ? r.first_live_page[g] : kept;
             if (first > old) {
                 int32_t* row = grp.tables.data() + (size_t)r.slot * max_pages_;
                 int bad = 0;

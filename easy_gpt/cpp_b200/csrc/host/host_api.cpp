@@ -39,6 +39,10 @@ EGH_API void egh_cache_destroy(void* c) { delete static_cast<CacheCore*>(c); }
 EGH_API int egh_cache_add_group(void* c, int num_pages, int window) {
     return num_pages > 0 ? static_cast<CacheCore*>(c)->add_group(num_pages, window) : BAD_ARGUMENT;
 }
+// a windowed group that keeps the first `keep_first` positions of every request for good
+EGH_API int egh_cache_add_group_keep(void* c, int num_pages, int window, int keep_first) {
+    return num_pages > 0 && keep_first >= 0 ? static_cast<CacheCore*>(c)->add_group(num_pages, window, keep_first) : BAD_ARGUMENT;
+}
 // borrowed: lives as long as the cache
 EGH_API void* egh_cache_group_pool(void* c, int g) { return &static_cast<CacheCore*>(c)->group(g).pool; }
 EGH_API int32_t* egh_cache_group_table(void* c, int g) { return static_cast<CacheCore*>(c)->group(g).tables.data(); }
