@@ -552,7 +552,7 @@ inline ModelSpec masezen_spec(const json::Value& config) {
 
 // ---- Mozalix ---------------------------------------------------------------------------------------------------------------
 // A decoder whose config.json lists its layers one by one.  A layer's branches read the stream itself and are normed on their
-// way back into it, x = x + n1(mixer(x)), x = x + n2(ff(x)), with RMS norms whose gains are stored around zero (1 + w).  The
+// way back into it, x = x + n1(mixer(x)), x = x + n2(ff(x)), with RMS norms whose tensors hold the gain minus one.  The
 // mixer is one of three: "attention" (grouped heads, q and k normed per head with a shared gain and then turned, keys of the
 // query's own block of mask.size positions, a learned sink per head), "attention_2" (two softmax maps a head over a sliding
 // window, the second taken off the first with one weight for the layer, the difference normed per head) and "parallel" (an

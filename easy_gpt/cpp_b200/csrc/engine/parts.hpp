@@ -257,7 +257,7 @@ public:
     void load(const HostTensors& file, DType) override {
         std::vector<float> g = host_floats(need_tensor(file, weight_name_));       // gains are used in float32 whatever they were stored in
         if (single_) g.assign((size_t)size_, g.at(0));                               // one number for all coordinates: the kernels read a gain per channel
-        if (offset_ != 0.f)                                                          // a gain stored around zero: the kernels read offset + w
+        if (offset_ != 0.f)                                                          // the tensor holds the gain's distance from the offset: the kernels read offset + w
             for (float& v : g) v += offset_;
         gain_ = upload(g.data(), g.size(), DType::F32);
     }
@@ -294,7 +294,7 @@ private:
     float eps_;
     std::string weight_name_;      // parameter weight_name: the gain's tensor name as a suffix of the prefix (default ".weight")
     bool single_;                  // parameter single_gain: the tensor is ONE number, the gain of every coordinate
-    float offset_;                 // parameter offset: the gain is offset + the stored tensor (1 for a gain stored around zero)
+    float offset_;                 // parameter offset: the gain is offset + the stored tensor (1 where the file holds the gain minus one)
     DeviceBuffer gain_;
 };
 

@@ -257,6 +257,77 @@ int main(int argc, char** argv) {
         CHECK(throws<std::invalid_argument>([&] { bad.validate(); }, "names stream addition 3"));
     }
 
+    // ---- a fourth listed design: branches normed on their way back, masks of three kinds, two mixers side by side, shared tensors ----
+    {
+        const char* kMasks = R"({"architecture": "Mozalix", "vocab": 77, "width": 56, "norm": {"eps": 4e-6}, "embedding": {"scale": 0.25},
+          "layers": [
+            {"type": "attention_2", "mixer": {"heads": 6, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.2, "diff": 0.3, "mask": {"size": 21},
+                                              "rot": {"base": 7000.0, "dims": 6}},
+             "mlp": {"kind": "dense", "ff": 72, "limit": 2.25}},
+            {"type": "parallel", "mixer": {"left": {"heads": 4, "kv_heads": 4, "dim": 8, "vdim": 12, "scale": 0.35, "softcap": 11.0, "mask": {"size": 17, "keep_first": 3}},
+                                           "right": {"heads": 4, "kv_heads": 2, "dim": 12, "vdim": 20, "conv": 3}, "left_scale": 0.75, "right_scale": 1.5},
+             "mlp": null},
+            {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.5, "mask": {"size": 13}}, "mlp": {"kind": "dense", "ff": 40, "limit": 1.0}},
+            {"type": "parallel", "weights_of": 1,
+             "mixer": {"left": {"heads": 4, "kv_heads": 4, "dim": 8, "vdim": 12, "scale": 0.35, "softcap": 11.0, "mask": {"size": 17, "keep_first": 3}},
+                       "right": {"heads": 4, "kv_heads": 2, "dim": 12, "vdim": 20, "conv": 3}, "left_scale": 0.75, "right_scale": 1.5},
+             "mlp": null},
+            {"type": "attention_2", "weights_of": 0, "mixer": {"heads": 6, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.2, "diff": 0.3, "mask": {"size": 21},
+                                                               "rot": {"base": 7000.0, "dims": 6}},
+             "mlp": {"kind": "dense", "ff": 72, "limit": 2.25}}]})";
+        const ModelSpec spec = ArchitectureRegistry::instance().build(json::parse(kMasks));
+        // three layers have tensors; five run, each with a cache of its own
+        CHECK(spec.architecture == "mozalix" && spec.layers.size() == 3 && spec.vocab_size == 77 && spec.hidden_size == 56 && spec.run_order.size() == 5);
+        const int layers[] = {0, 1, 2, 1, 0};
+        for (int i = 0; i < 5; ++i) CHECK(spec.run_order[i].layer == layers[i] && spec.run_order[i].cache == i && spec.run_order[i].writes_cache);
+        CHECK(spec.embedding.params.real("scale") == 0.25 && spec.final_norm.params.real("offset") == 1.0 && spec.final_norm.prefix == "final.norm");
+        // no norm in front of a branch, one with the gain kept as its distance from one behind it
+        const SubLayerSpec& mix = spec.layers[0].sublayers[0];
+        CHECK(!mix.norm.present && mix.output_norm.kind == "rmsnorm" && mix.output_norm.prefix == "l0.norm1" && mix.output_norm.params.real("offset") == 1.0 &&
+              mix.output_norm.params.real("eps") == 4e-6 && !spec.layers[0].parallel);
+        CHECK(mix.part.kind == "masked_attention" && mix.part.prefix == "l0.mix" && mix.part.params.integer("maps") == 2 && mix.part.params.integer("window") == 21 &&
+              !mix.part.params.has("chunk") && mix.part.params.real("diff") == 0.3 && mix.part.params.text("qk_norm") == "gain" && mix.part.params.real("norm_eps") == 4e-6 &&
+              mix.part.params.integer("heads") == 6 && mix.part.params.integer("kv_heads") == 2 && mix.part.params.integer("vdim") == 24);
+        CHECK(spec.layers[0].position.present && spec.layers[0].position.params.integer("rotary_dim") == 6 && spec.layers[0].position.params.real("theta") == 7000.0);
+        const SubLayerSpec& ff = spec.layers[0].sublayers[1];
+        CHECK(ff.part.kind == "swiglu" && ff.part.params.text("activation") == "clamped" && ff.part.params.real("limit") == 2.25 && ff.part.params.flag("bias", false) &&
+              ff.part.params.integer("intermediate_size") == 72 && ff.part.params.text("gate_bias_name") == ".gate.b" && !ff.norm.present &&
+              ff.output_norm.prefix == "l0.norm2");
+        // the two mixers side by side carry their own parameters, the sum's weights among them
+        const PartSpec& both = spec.layers[1].sublayers[0].part;
+        CHECK(spec.layers[1].sublayers.size() == 1 && both.kind == "side_by_side" && both.params.text("left_kind") == "masked_attention" &&
+              both.params.text("right_kind") == "channel_delta");
+        const Params left = both.params.sub("left."), right = both.params.sub("right.");
+        CHECK(left.integer("window") == 17 && left.integer("keep_first") == 3 && left.real("softcap") == 11.0 && left.text("qk_norm") == "unit" &&
+              left.real("out_scale") == 0.75 && !left.has("maps") && !left.has("sinks") && !spec.layers[1].position.present);
+        CHECK(right.integer("heads") == 4 && right.integer("kv_heads") == 2 && right.integer("dim") == 12 && right.integer("vdim") == 20 && right.integer("conv") == 3 &&
+              right.real("out_scale") == 1.5 && right.text("gate") == "sigmoid" && right.real("unit_eps") == 1e-6 && !right.has("rank"));
+        const PartSpec& chunks = spec.layers[2].sublayers[0].part;
+        CHECK(chunks.params.integer("chunk") == 13 && !chunks.params.has("window") && chunks.params.integer("sinks") == 1 && !spec.layers[2].position.present);
+        auto changed = [&](const std::string& from, const std::string& to) {
+            std::string text = kMasks;
+            const size_t at = text.find(from);
+            CHECK(at != std::string::npos);
+            text.replace(at, from.size(), to);
+            return text;
+        };
+        // no mask: all keys; no embedding entry: no scale
+        const ModelSpec open_mask = ArchitectureRegistry::instance().build(json::parse(changed(R"(, "mask": {"size": 13})", "")));
+        CHECK(!open_mask.layers[2].sublayers[0].part.params.has("chunk"));
+        const ModelSpec unscaled = ArchitectureRegistry::instance().build(json::parse(changed(R"("embedding": {"scale": 0.25},)", "")));
+        CHECK(!unscaled.embedding.params.has("scale"));
+        for (const auto& wrong : {changed(R"("weights_of": 1)", R"("weights_of": 0)"), changed(R"("weights_of": 1)", R"("weights_of": 9)"),
+                                  changed(R"("type": "attention",)", R"("type": "attention_3",)"), changed(R"("limit": 1.0)", R"("limit": 0)")}) {
+            bool refused = false;
+            try {
+                ArchitectureRegistry::instance().build(json::parse(wrong));
+            } catch (const std::exception&) {
+                refused = true;
+            }
+            CHECK(refused);
+        }
+    }
+
     // ---- a third listed design: one norm a layer read by two branches side by side, a convolution in front of the mixer, a token input behind --
     {
         const char* kSide = R"({"architecture": "Masezen", "vocab": 91, "width": 40, "norm": {"eps": 3e-6}, "canon": {"taps": 5}, "token_side": {"dim": 7},

@@ -58,6 +58,37 @@ static void cache_with_a_window() {
     CHECK(cache.group(full).pool.free_count() == 32 && cache.group(win).pool.free_count() == 32);
 }
 
+// a window that also keeps a request's first positions: the pages that hold them stay, the window's release starts behind them
+static void cache_with_a_window_and_kept_first_positions() {
+    for (int keep : {1, 4, 6, 13}) {
+        CacheCore cache(4, 2, 64);
+        const int win = cache.add_group(32, 10, keep), plain = cache.add_group(32, 10);
+        const int kept_pages = (keep + 3) / 4;
+        CHECK(cache.begin_request(3) == 0);
+        int pos = 0;
+        for (int count : {1, 1, 7, 2, 30, 1, 1, 1, 16, 3}) {         // portions and single tokens
+            CHECK(cache.reserve(3, count, nullptr) == OK && cache.commit(3, count) == OK);
+            pos += count;                                            // the next token sits at pos and sees keys pos - 9 .. pos and 0 .. keep - 1
+            const int first_key = pos - 10 + 1 > 0 ? pos - 10 + 1 : 0;
+            const int32_t* row = cache.group(win).tables.data();
+            const int32_t* bare = cache.group(plain).tables.data();
+            for (int i = 0; i < 64; ++i) {
+                const bool written = i <= (pos - 1) / 4;
+                CHECK((row[i] >= 0) == (written && (i >= first_key / 4 || i < kept_pages)));
+                CHECK((bare[i] >= 0) == (written && i >= first_key / 4));
+            }
+        }
+        std::string why;
+        CHECK(cache.check(&why) == OK);
+        CHECK(cache.end_request(3) == OK);
+        CHECK(cache.group(win).pool.free_count() == 32 && cache.group(plain).pool.free_count() == 32);
+        // the slot and its pages serve the next request from its first position
+        CHECK(cache.begin_request(4) == 0 && cache.reserve(4, 9, nullptr) == OK && cache.commit(4, 9) == OK);
+        CHECK(cache.group(win).tables[0] >= 0 && cache.group(win).tables[2] >= 0 && cache.group(win).tables[3] < 0);
+        CHECK(cache.end_request(4) == OK);
+    }
+}
+
 static void a_step_is_reserved_whole_or_not_at_all() {
     CacheCore cache(4, 3, 16);
     cache.add_group(6, -1);
@@ -150,6 +181,7 @@ int main() {
     the_tokenizer_follows_the_rules();
     pools();
     cache_with_a_window();
+    cache_with_a_window_and_kept_first_positions();
     a_step_is_reserved_whole_or_not_at_all();
     the_scheduler_finishes_everything_although_pages_run_out();
     std::puts("host runtime: all checks passed");

@@ -36,7 +36,7 @@ def rms_unit(x, eps):
 
 
 def offset_norm(y, gain, eps):
-    """The layer's norm: a gain stored around zero."""
+    """The layer's norm: the tensor holds the gain's distance from one."""
     return rms_unit(y, eps) * (1.0 + gain)
 
 
@@ -82,6 +82,14 @@ def seen_window(n, size, keep_first=0):
     return (j <= i) & ((i - j < size) | (j < keep_first))
 
 
+def seen_by(n, m, kind):
+    """The mask of a mixer's configuration; without a "mask" entry every earlier key is seen."""
+    mask = m.get("mask")
+    if not mask:
+        return seen_window(n, n)
+    return seen_chunk(n, mask["size"]) if kind == "chunk" else seen_window(n, mask["size"], mask.get("keep_first", 0))
+
+
 def softmax_rows(s, seen, sink=None):
     """Weights over the seen keys of every row; a sink is one more term of the sum, with no key and no value."""
     s = np.where(seen, s, -np.inf)
@@ -107,7 +115,7 @@ def chunked_sink_attention(h, w, p, m, eps):
     v = (h @ w[p + "v"].T).reshape(n, G, dv)
     q = rotate_half(rms_unit(q, eps) * w[p + "q.norm"], pos, m.get("rot"))
     k = rotate_half(rms_unit(k, eps) * w[p + "k.norm"], pos, m.get("rot"))
-    seen = seen_chunk(n, m["mask"]["size"])
+    seen = seen_by(n, m, "chunk")
     out = np.zeros((n, H, dv))
     for head in range(H):
         g = head // (H // G)
@@ -131,7 +139,7 @@ def differential_attention(h, w, p, m, eps):
     v = (h @ w[p + "v"].T).reshape(n, G, dv)
     q = rotate_half(rms_unit(q, eps) * w[p + "q.norm"], pos, m.get("rot"))
     k = rotate_half(rms_unit(k, eps) * w[p + "k.norm"], pos, m.get("rot"))
-    seen = seen_window(n, m["mask"]["size"])
+    seen = seen_by(n, m, "window")
     lam = differential_lambda(w, p, m)
     out = np.zeros((n, H, dv))
     for head in range(H):
@@ -152,13 +160,14 @@ def capped_window_attention(h, w, p, m, eps):
     q = rms_unit((h @ w[p + "q"].T).reshape(n, H, dk), eps)
     k = rms_unit((h @ w[p + "k"].T).reshape(n, G, dk), eps)
     v = (h @ w[p + "v"].T).reshape(n, G, dv)
-    seen = seen_window(n, m["mask"]["size"], m["mask"].get("keep_first", 0))
-    cap = m["softcap"]
+    seen = seen_by(n, m, "window")
+    cap = m.get("softcap")
     out = np.zeros((n, H, dv))
     for head in range(H):
         g = head // (H // G)
         s = (q[:, head] @ k[:, g].T) * m["scale"]
-        s = cap * np.tanh(s / cap)
+        if cap:
+            s = cap * np.tanh(s / cap)
         out[:, head] = softmax_rows(s, seen) @ v[:, g]
     return out.reshape(n, H * dv) @ w[p + "o"].T
 
@@ -238,17 +247,18 @@ def attention_shapes(p, m, d, maps):
     return {p + "q": (H * maps * dk, d), p + "k": (G * maps * dk, d), p + "v": (G * dv, d), p + "o": (d, H * dv)}
 
 
-def delta_shapes(p, m, d):
+def delta_shapes(p, m, d, rank):
     H, G, dk, dv, K = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
-    r = m.get("rank", None)
+    ra, rg = rank if isinstance(rank, tuple) else (rank, rank)
     return {p + "q": (G * dk, d), p + "q.conv": (G * dk, K), p + "k": (G * dk, d), p + "k.conv": (G * dk, K), p + "v": (H * dv, d),
-            p + "v.conv": (H * dv, K), p + "b": (H, d), p + "A_log": (H,), p + "norm": (dv,), p + "a1": (r, d), p + "a2": (H * dk, r),
-            p + "dt_bias": (H * dk,), p + "g1": (r, d), p + "g2": (H * dv, r), p + "o": (d, H * dv)}
+            p + "v.conv": (H * dv, K), p + "b": (H, d), p + "A_log": (H,), p + "norm": (dv,), p + "a1": (ra, d), p + "a2": (H * dk, ra),
+            p + "dt_bias": (H * dk,), p + "g1": (rg, d), p + "g2": (H * dv, rg), p + "o": (d, H * dv)}
 
 
 def tensor_shapes(config, ranks=None):
-    """name -> shape of every tensor a model of this configuration has.  The inner size of the two-step maps of a delta
-    mixer is no key of the configuration (a tensor's shape gives it): ``ranks`` maps a layer index to it (default 8)."""
+    """name -> shape of every tensor a model of this configuration has.  The inner sizes of the two-step maps of a delta
+    mixer are no keys of the configuration (the tensors' shapes give them): ``ranks`` maps a layer index to one size for
+    both maps or to a pair (decay map, gate map); default 8."""
     d, V = config["width"], config["vocab"]
     shapes = {"embed": (V, d), "final.norm": (d,), "head": (V, d)}
     for i, layer in enumerate(config["layers"]):
@@ -265,7 +275,7 @@ def tensor_shapes(config, ranks=None):
                 shapes[p + "mix." + name] = (m["dim"],)
         else:
             shapes.update(attention_shapes(p + "mix.left.", m["left"], d, 1))
-            shapes.update(delta_shapes(p + "mix.right.", dict(m["right"], rank=(ranks or {}).get(i, 8)), d))
+            shapes.update(delta_shapes(p + "mix.right.", m["right"], d, (ranks or {}).get(i, 8)))
         mlp = layer.get("mlp")
         if mlp:
             shapes[p + "norm2"] = (d,)
@@ -290,7 +300,7 @@ def random_weights(config, seed, overrides=None, ranks=None):
     for name, shape in tensor_shapes(config, ranks).items():
         leaf = name.split(".")[-1]
         if leaf in ("norm1", "norm2") or name == "final.norm":
-            v = 0.2 * rng.standard_normal(shape)                 # stored around zero
+            v = 0.2 * rng.standard_normal(shape)                 # the gain is one plus this
         elif leaf == "norm":
             v = 1.0 + 0.2 * rng.standard_normal(shape)           # q.norm, k.norm, the delta mixer's output gain
         elif leaf == "sink":
