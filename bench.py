@@ -30,6 +30,7 @@ For profiling and for further sizes (one short line each, never the JSON line ab
     python bench.py --only decode|prefill|timeline|gemm|attention|serve [--batch B] [--layers L] [--context C] [--sizes 0.5b|1.5b|7b]
     python bench.py --only gufanex [--batch B] [--context C] [--steps K] [--sizes small|medium]
     python bench.py --only lasizen [--batch B] [--context C] [--steps K] [--sizes small|medium]
+    python bench.py --only mozalix [--batch B] [--context C] [--steps K] [--sizes small|medium] [--model both|mozalix|lasizen]
 
 `gufanex` measures the Gufanex decoder (selective-scan and latent-attention layers with routed experts) at layer sizes
 of real models of those kinds, with random weights, beside a Qwen2 decoder of the same width, depth and active
@@ -38,6 +39,10 @@ feed-forward size: one prompt of 2,048 tokens as one step, and decode steps of a
 `lasizen` measures the Lasizen decoder (windowed attention with a sink, gated delta-rule mixers, xIELU feed-forwards,
 norms on both sides of every branch) the same way, beside a Qwen2 decoder of the same width, depth, heads and
 feed-forward weights.
+
+`mozalix` measures the Mozalix decoder (attention with two softmax maps a head, attention in chunks with sinks, a windowed
+attention that keeps first tokens beside a delta-rule mixer with a decay per key channel, gated feed-forwards with limits and
+biases) the same way, beside the Lasizen decoder of the same width, layer runs and heads.
 
 `serve` runs 64 concurrent requests (prompts of 128..4096 tokens in portions of 512 beside
 decoding requests, 512 new tokens each) through the engine and reports wall-clock tokens a second.
@@ -129,6 +134,31 @@ def masezen_bench_configs(size):
     qwen = dict(CONFIG_05B, num_hidden_layers=6, hidden_size=width, num_attention_heads=heads, num_key_value_heads=4 // k, head_dim=128,
                 intermediate_size=4 * ff, vocab_size=32000, tie_word_embeddings=False)
     return masezen, qwen
+
+
+# Layer sizes for `--only mozalix`: width 2,048; an attention of 8 heads with two softmax maps each (keys of 128, values of 128, 4
+# key heads) over a window of 1,024; a layer of two mixers side by side (an attention of 8 heads of 128 over 4 key heads with a
+# window of 1,024 that keeps the first 64 tokens and capped scores, beside a delta-rule mixer of 8 heads with 128 x 128 states and
+# a decay per key channel through maps of inner size 64); an attention of 16 heads of 128 over 4 key heads in chunks of 1,024 with
+# sinks; a gated feed-forward with as many weights as four times the width in two maps ("medium"), and half of the width, heads
+# and feed-forward ("small").  Three layers with tensors, each run twice: six layer runs.  Beside it the closest existing model,
+# the Lasizen decoder of `--only lasizen` (windowed attention with a sink, delta-rule mixers): same width, layer runs and heads.
+def mozalix_bench_configs(size):
+    k = {"medium": 1, "small": 2}[size]
+    width, heads = 2048 // k, 16 // k
+    two = {"type": "attention_2", "mixer": {"heads": heads // 2, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "diff": 0.4, "mask": {"size": 1024},
+                                            "rot": {"base": 500000.0, "dims": 64}}}
+    pair = {"type": "parallel", "mixer": {"left": {"heads": heads // 2, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                                                   "mask": {"size": 1024, "keep_first": 64}},
+                                          "right": {"heads": heads // 2, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "conv": 4, "rank": 64},
+                                          "left_scale": 0.7, "right_scale": 0.7}}
+    chunks = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 4 // k, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                                             "rot": {"base": 500000.0, "dims": 64}}}
+    mlp = {"kind": "dense", "ff": (8 * width // 3 + 127) // 128 * 128, "limit": 7.0}
+    layers = [dict(two, mlp=mlp), dict(pair, mlp=mlp), dict(chunks, mlp=mlp)]
+    layers += [dict(layers[j], weights_of=j) for j in range(3)]
+    mozalix = {"architecture": "Mozalix", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": float(width) ** 0.5}, "layers": layers}
+    return mozalix, lasizen_bench_configs(size)[0]
 
 
 CONTEXT = 4096
@@ -316,6 +346,8 @@ def gufanex_folder(config, seed=0):
         from easy_gpt.cpp_b200.weights.lasizen_init import write_random_model
     elif config.get("architecture") == "Masezen":
         from easy_gpt.cpp_b200.weights.masezen_init import write_random_model
+    elif config.get("architecture") == "Mozalix":
+        from easy_gpt.cpp_b200.weights.mozalix_init import write_random_model
     else:
         from easy_gpt.cpp_b200.weights.gufanex_init import write_random_model
 
@@ -662,7 +694,25 @@ def run_masezen(args):
     return 0
 
 
+def run_mozalix(args):
+    size = args.sizes if args.sizes in ("small", "medium") else "medium"
+    mozalix, lasizen = mozalix_bench_configs(size)
+    context = min(args.context, 2048) if args.context == CONTEXT else args.context
+    out = {"only": "mozalix", "sizes": size, "batch": args.batch, "context": context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bfloat16",
+           "data": "synthetic (random weights)"}
+    with ClockSampler() as clocks:
+        if args.model in ("both", "mozalix"):
+            out["mozalix"] = measure_prefill_and_decode(gufanex_folder(mozalix), mozalix["vocab"], args.batch, context, args.steps, args.warmup)
+        if args.model in ("both", "lasizen"):
+            out["lasizen_equal"] = measure_prefill_and_decode(gufanex_folder(lasizen), lasizen["vocab"], args.batch, context, args.steps, args.warmup)
+    out["clocks"] = clocks.summary()
+    print(json.dumps(out))
+    return 0
+
+
 def run_ours(args):
+    if args.only == "mozalix":
+        return run_mozalix(args)
     if args.only == "gufanex":
         return run_gufanex(args)
     if args.only == "masezen":
@@ -796,16 +846,16 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length the decode steps end at (default 4096)")
-    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex, --only lasizen and --only masezen)")
-    ap.add_argument("--model", choices=["both", "gufanex", "lasizen", "masezen", "qwen2"], default="both",
-                    help="with --only gufanex, --only lasizen or --only masezen: which of the two models to measure")
+    ap.add_argument("--sizes", choices=list(SIZES) + ["small", "medium"], default="0.5b", help="layer sizes for --only runs (small, medium: --only gufanex, --only lasizen, --only masezen and --only mozalix)")
+    ap.add_argument("--model", choices=["both", "gufanex", "lasizen", "masezen", "mozalix", "qwen2"], default="both",
+                    help="with --only gufanex, --only lasizen, --only masezen or --only mozalix: which of the two models to measure")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16", help="precision of --only decode")
     ap.add_argument("--default-options", action="store_true",
                     help="--only decode with the engine's default page size and request length")
     ap.add_argument("--ref-prompt", type=int, default=0,
                     help="prompt length of the reference arm (0: 1536, or the longest its int-indexed logits allow)")
     ap.add_argument("--fused", action="store_true", help="with --only timeline or decode: the decode step as one persistent kernel (EASY_GPT_FUSED_DECODE=1)")
-    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex", "lasizen", "masezen"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "timeline", "gemm", "attention", "serve", "gufanex", "lasizen", "masezen", "mozalix"], default=None,
                     help="measure one part only and print a short line (for profiling runs)")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -561,6 +561,30 @@ inline ModelSpec masezen_spec(const json::Value& config) {
 // feed-forward is a gated one with clamped gate and up values and biases on all three maps, or none.  A layer with
 // "weights_of": j runs layer j's tensors on a cache and state of its own.  The embedding is scaled by embedding.scale.  Every
 // size and constant is a key of config.json; tensor names are "l<i>.<part>.<tensor>".
+// whether two values of a configuration say the same (members of an object in any order)
+inline bool same_config_value(const json::Value& a, const json::Value& b) {
+    if (a.type != b.type) return false;
+    switch (a.type) {
+        case json::Value::Null: return true;
+        case json::Value::Bool: return a.boolean == b.boolean;
+        case json::Value::Number: return a.number == b.number;
+        case json::Value::String: return a.string == b.string;
+        case json::Value::Array:
+            if (a.array.size() != b.array.size()) return false;
+            for (size_t i = 0; i < a.array.size(); ++i)
+                if (!same_config_value(a.array[i], b.array[i])) return false;
+            return true;
+        case json::Value::Object:
+            if (a.object.size() != b.object.size()) return false;
+            for (auto& kv : a.object) {
+                const json::Value* other = b.find(kv.first);
+                if (!other || !same_config_value(kv.second, *other)) return false;
+            }
+            return true;
+    }
+    return false;
+}
+
 inline ModelSpec mozalix_spec(const json::Value& config) {
     using C = GufanexConfig;        // the typed readers (a key's path goes into the refusal)
     if (!config.is_object()) throw ConfigError("config.json is not a JSON object");
@@ -691,6 +715,13 @@ inline ModelSpec mozalix_spec(const json::Value& config) {
             const json::Value &mine = C::need(l, "type", "layers[" + std::to_string(i) + "]."), &theirs = C::need(layers.array[owner[i]], "type", "");
             if (!mine.is_string() || mine.string != theirs.string)
                 throw ConfigError("layers[" + std::to_string(i) + "] uses the tensors of a layer of another type");
+            // one set of parts runs both layers: sizes and constants that differed would be ignored without a word
+            static const json::Value none;
+            for (const char* key : {"mixer", "mlp"}) {
+                const json::Value *a = l.find(key), *b = layers.array[owner[i]].find(key);
+                if (!same_config_value(a ? *a : none, b ? *b : none))
+                    throw ConfigError("layers[" + std::to_string(i) + "]." + key + " differs from that of the layer whose tensors it uses");
+            }
         }
         spec.run_order.push_back(RunEntry{built[owner[i]], (int)i, true});
     }

@@ -317,7 +317,9 @@ int main(int argc, char** argv) {
         const ModelSpec unscaled = ArchitectureRegistry::instance().build(json::parse(changed(R"("embedding": {"scale": 0.25},)", "")));
         CHECK(!unscaled.embedding.params.has("scale"));
         for (const auto& wrong : {changed(R"("weights_of": 1)", R"("weights_of": 0)"), changed(R"("weights_of": 1)", R"("weights_of": 9)"),
-                                  changed(R"("type": "attention",)", R"("type": "attention_3",)"), changed(R"("limit": 1.0)", R"("limit": 0)")}) {
+                                  changed(R"("type": "attention",)", R"("type": "attention_3",)"), changed(R"("limit": 1.0)", R"("limit": 0)"),
+                                  // the entry of a layer that runs another's tensors must equal that layer's (here the first of the two is changed)
+                                  changed(R"("size": 17, "keep_first": 3)", R"("size": 18, "keep_first": 3)")}) {
             bool refused = false;
             try {
                 ArchitectureRegistry::instance().build(json::parse(wrong));
