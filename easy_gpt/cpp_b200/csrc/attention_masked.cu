@@ -7,6 +7,10 @@
 // rows are [tokens, H * maps, dk], row h * maps + m being map m of head h.  KV head g = h / (H / G) holds `maps` keys of dk
 // values side by side and ONE value of dv values, which all maps share.  The output has a row per (head, map).
 //
+// With `planes` (keys and values in planes of their own, which holds for dk = dv only) both planes have G * maps heads: key
+// head g * maps + m is map m's key of head g, and the value of head g is stored once per map, so that a kernel that knows
+// nothing of maps sees G * maps ordinary key/value heads.
+//
 // Preparation, per token at position p (float32 throughout, from the float32 output of the projections):
 //   norm_eps >= 0: every query and key (per head and map) is divided by its root mean square over dk (eps under the root)
 //   and, with a gain [dk] given, multiplied by it channel by channel;
@@ -38,7 +42,7 @@ __global__ void __launch_bounds__(128) masked_prepare_kernel(const float* __rest
                                                              T* __restrict__ v_cache, int row_stride, long long head_stride, int page_size,
                                                              long long page_stride, long long pool_slots, T* __restrict__ q_out, int tokens, int heads,
                                                              int kv_heads, int maps, int dk, int dv, float norm_eps, const float* __restrict__ q_gain,
-                                                             const float* __restrict__ k_gain, int* status) {
+                                                             const float* __restrict__ k_gain, int planes, int* status) {
     const int lane = threadIdx.x & 31;
     const int Q = heads * maps, K = kv_heads * maps, rows = Q + K + kv_heads;
     const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -52,17 +56,19 @@ __global__ void __launch_bounds__(128) masked_prepare_kernel(const float* __rest
             if (lane == 0) atomicOr(status, EG_STATUS_BAD_SLOT);
             return;
         }
-        const int g = r < Q + K ? (r - Q) / maps : r - Q - K;
+        // the cache head: the key/value head, or with planes the (head, map) pair (a value then starts at its head's first map)
+        const int g = r < Q + K ? (planes ? r - Q : (r - Q) / maps) : (planes ? (r - Q - K) * maps : r - Q - K);
         at = (slot / page_size) * page_stride + g * head_stride + (slot % page_size) * (long long)row_stride;
     }
-    if (r >= Q + K) {                               // a value: stored as it is
+    if (r >= Q + K) {                               // a value: stored as it is (with planes once per map)
         const float* v = proj + (size_t)t * ld + (size_t)(Q + K) * dk + (size_t)(r - Q - K) * dv;
-        for (int d = lane; d < dv; d += 32) v_cache[at + d] = from_f32<T>(v[d]);
+        for (int c = 0; c < (planes ? maps : 1); ++c)
+            for (int d = lane; d < dv; d += 32) v_cache[at + c * head_stride + d] = from_f32<T>(v[d]);
         return;
     }
     const float* src = proj + (size_t)t * ld + (size_t)r * dk;          // queries then keys, row after row
     const float* gain = r < Q ? q_gain : k_gain;
-    T* dst = r < Q ? q_out + ((size_t)t * Q + r) * dk : k_cache + at + (size_t)((r - Q) % maps) * dk;
+    T* dst = r < Q ? q_out + ((size_t)t * Q + r) * dk : k_cache + at + (planes ? 0 : (size_t)((r - Q) % maps) * dk);
     float inv = 1.0f;
     if (norm_eps >= 0.f) {
         float ss = 0.f;
@@ -92,14 +98,15 @@ masked_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq, const int* __restrict__ positions,
                         const int* __restrict__ token_list, TO* __restrict__ out, long long ldo, int heads, int kv_heads, int maps, int dk, int dv,
                         int page_size, long long page_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap,
-                        const float* __restrict__ sinks, float out_scale, int* status) {
+                        const float* __restrict__ sinks, float out_scale, int planes, int* status) {
     extern __shared__ float q_shared[];              // WARPS * dk
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = token_list ? token_list[blockIdx.x] : blockIdx.x;
     const int r = blockIdx.y * WARPS + warp;          // the query row: head * maps + map
     if (r >= heads * maps) return;                    // no block-wide barrier below
     const int h = r / maps, map = r % maps;
-    const int g = h / (heads / kv_heads);
+    const int g = planes ? h / (heads / kv_heads) * maps + map : h / (heads / kv_heads);        // the cache head
+    const int key_at = planes ? 0 : map * dk;
     const int pos = positions[t];
     const int* table = block_table + (size_t)token_seq[t] * table_stride;
     float* qs = q_shared + warp * dk;
@@ -127,7 +134,7 @@ masked_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             }
             float s = -INFINITY;
             if (row_off >= 0) {
-                const T* krow = k_cache + row_off + (size_t)map * dk;
+                const T* krow = k_cache + row_off + key_at;
                 float dot = 0.0f;
                 for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], to_f32<T>(krow[d]), dot);
                 s = dot * scale;
@@ -202,23 +209,24 @@ __global__ void __launch_bounds__(128) map_difference_kernel(const float* __rest
 
 // proj float32 [tokens, ld]: heads * maps queries, kv_heads * maps keys (dk values each), kv_heads values (dv each), side by
 // side.  table: cos/sin [tokens, rot_dims/2, 2] or null with rot_dims 0.  norm_eps < 0: no norm; q_gain / k_gain float32 [dk] or
-// null.  k_cache null: nothing is stored.  q_out [tokens, heads * maps, dk].
+// null.  k_cache null: nothing is stored.  q_out [tokens, heads * maps, dk].  planes: see above.
 EG_API int eg_masked_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude,
                                        const int* slot_map, void* k_cache, void* v_cache, int row_stride, long long head_stride, int page_size,
                                        long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int maps, int dk, int dv,
-                                       float norm_eps, const float* q_gain, const float* k_gain, int* status) {
+                                       float norm_eps, const float* q_gain, const float* k_gain, int planes, int* status) {
     if (tokens <= 0) return 0;
+    if (planes && dk != dv) return (int)cudaErrorInvalidValue;
     if (rot_dims < 0 || rot_dims % 2 || rot_dims > dk || (rot_dims > 0 && !table) || maps < 1 || kv_heads <= 0 || heads % kv_heads) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)tokens * ((heads + kv_heads) * maps + kv_heads);
     const unsigned blocks = (unsigned)((warps + 3) / 4);
     if (dtype == EG_BF16)
         masked_prepare_kernel<bf16><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (bf16*)k_cache, (bf16*)v_cache,
                                                                 row_stride, head_stride, page_size, page_stride, pool_slots, (bf16*)q_out, tokens, heads, kv_heads,
-                                                                maps, dk, dv, norm_eps, q_gain, k_gain, status);
+                                                                maps, dk, dv, norm_eps, q_gain, k_gain, planes, status);
     else
         masked_prepare_kernel<float><<<blocks, 128, 0, stream>>>(proj, ld, (const float2*)table, rot_dims / 2, magnitude, slot_map, (float*)k_cache, (float*)v_cache,
                                                                  row_stride, head_stride, page_size, page_stride, pool_slots, (float*)q_out, tokens, heads, kv_heads,
-                                                                 maps, dk, dv, norm_eps, q_gain, k_gain, status);
+                                                                 maps, dk, dv, norm_eps, q_gain, k_gain, planes, status);
     return eg_launch_status();
 }
 
@@ -229,7 +237,7 @@ EG_API int eg_masked_attention(cudaStream_t stream, int dtype, const void* q, co
                                const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out,
                                int out_dtype, long long ldo, int num_tokens, int heads, int kv_heads, int maps, int dk, int dv, int page_size,
                                long long page_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks,
-                               float out_scale, int* status) {
+                               float out_scale, int planes, int* status) {
     if (num_tokens <= 0) return 0;
     if (dv > 32 * MAX_PER_LANE || dv <= 0 || dk <= 0 || dk > 4096 || kv_heads <= 0 || heads % kv_heads || maps < 1 || keep_first < 0) return (int)cudaErrorInvalidValue;
     if (dtype == EG_F32 && out_dtype != EG_F32) return (int)cudaErrorInvalidValue;
@@ -239,7 +247,7 @@ EG_API int eg_masked_attention(cudaStream_t stream, int dtype, const void* q, co
     masked_attention_kernel<T, TO><<<grid, WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, row_stride, head_stride, block_table, \
                                                                        table_stride, token_seq, positions, token_list, (TO*)out, ldo, heads, kv_heads, maps, dk, \
                                                                        dv, page_size, page_stride, num_pages, window, chunk, keep_first, scale, softcap, sinks,  \
-                                                                       out_scale, status)
+                                                                       out_scale, planes, status)
     if (dtype == EG_BF16 && out_dtype == EG_BF16) EG_MASKED(bf16, bf16);
     else if (dtype == EG_BF16) EG_MASKED(bf16, float);
     else EG_MASKED(float, float);
@@ -256,5 +264,24 @@ EG_API int eg_attention_map_difference(cudaStream_t stream, const float* maps, v
     const unsigned blocks = (unsigned)((warps + 3) / 4);
     if (out_dtype == EG_BF16) map_difference_kernel<bf16><<<blocks, 128, 0, stream>>>(maps, (bf16*)out, ldo, tokens, heads, dv, lambda, eps, post);
     else map_difference_kernel<float><<<blocks, 128, 0, stream>>>(maps, (float*)out, ldo, tokens, heads, dv, lambda, eps, post);
+    return eg_launch_status();
+}
+
+namespace {
+__global__ void single_token_tiles_kernel(const int* __restrict__ token_list, const int* __restrict__ token_seq, int* __restrict__ tiles, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int t = token_list ? token_list[i] : i;
+    tiles[3 * i] = token_seq[t];
+    tiles[3 * i + 1] = t;
+    tiles[3 * i + 2] = 1;
+}
+}  // namespace
+
+// tiles int32 [n, 3] = (block table row, token, 1) for the tokens of token_list (or tokens 0 .. n - 1): single tokens in the form
+// in which the tiled attention kernels take prompt portions
+EG_API int eg_single_token_tiles(cudaStream_t stream, const int* token_list, const int* token_seq, int* tiles, int n) {
+    if (n <= 0) return 0;
+    single_token_tiles_kernel<<<(n + 127) / 128, 128, 0, stream>>>(token_list, token_seq, tiles, n);
     return eg_launch_status();
 }

@@ -631,7 +631,22 @@ struct PrefillParams {
     float scale;
     int* status;
     float sink2 = -INFINITY;      // as in Params
+    // Further masks and score functions (all off by default).  chunk: a query sees keys of its own block of `chunk` positions
+    // only; keep_first: keys 0 .. keep_first - 1 stay visible whatever window and chunk say; softcap c: the scaled score becomes
+    // c tanh(score / c); sinks: a logit per query row in place of sink2; maps m: rows h = head * m + map read key head
+    // (head / group) * m + map (both planes hold num_kv_heads heads); out_scale: a factor on the output; out_f32: the
+    // output goes there as float32 [tokens, ldo] instead of to `out`.
+    int chunk = 0, keep_first = 0, maps = 1;
+    float softcap = 0.f, out_scale = 1.f;
+    const float* sinks = nullptr;
+    float* out_f32 = nullptr;
 };
+
+// tanh by one exponent and one division: absolute error about 1e-7, which a score that goes into an exponent next can bear
+__device__ __forceinline__ float tanh_by_exp(float x) {
+    const float e = __expf(2.0f * fminf(x, 15.0f));
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
 
 template <int HD>
 struct PrefillLayout {
@@ -651,8 +666,10 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     const int item = gridDim.x - 1 - blockIdx.x;
     const int tile = item >> 1, half = item & 1;                 // a listed tile has up to 128 tokens: two CTAs
     const int h = blockIdx.y;
-    const int kvh = h / (p.num_heads / p.num_kv_heads);
-    const float scale_log2 = p.scale * 1.4426950408889634f;
+    const int kvh = (h / p.maps) / (p.num_heads / p.num_kv_heads) * p.maps + h % p.maps;
+    // with a soft cap the scores are scaled and capped as they come out of the product; else the scale rides in the exponent
+    const float scale_log2 = p.softcap > 0.f ? 1.4426950408889634f : p.scale * 1.4426950408889634f;
+    const float sink2 = p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1] + half * TILE_KEYS;
@@ -660,8 +677,18 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     if (count <= 0) return;
     const int* table = p.block_table + (size_t)seq * p.table_stride;
     const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;           // positions in a tile are consecutive
-    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int tile_lo = first / TILE_KEYS, ntiles = pos_hi / TILE_KEYS - tile_lo + 1;
+    // the first key that the window and the chunk of a query at `pos` leave visible (never decreasing in pos)
+    auto first_of = [&](int pos) {
+        const int w = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        return p.chunk > 0 ? max(w, pos / p.chunk * p.chunk) : w;
+    };
+    const int first = first_of(pos_lo);
+    const int tile_lo = first / TILE_KEYS;
+    // key tiles in the order they are walked: those of the kept first keys that lie wholly in front of the others, then the
+    // tiles from the first visible key on
+    const int kept_tiles = p.keep_first > 0 ? min((p.keep_first + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
+    const int ntiles = kept_tiles + pos_hi / TILE_KEYS - tile_lo + 1;
+    auto tile_of = [&](int it) { return it < kept_tiles ? it : tile_lo + it - kept_tiles; };
 
     // rows of this warp: r0 = warp*16 + gid, r1 = r0 + 8
     const int r0 = warp * 16 + gid, r1 = r0 + 8;
@@ -682,14 +709,14 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     }
 
     __shared__ long long quarter_base[QUARTER_TILES * 4];         // as in the decode kernel
-    int quarter_tile0 = tile_lo;
+    int quarter_tile0 = 0;                                        // in walking order
     auto fill_quarters = [&](int tile0) {
         quarter_tile0 = tile0;
-        const int count = min(QUARTER_TILES, tile_lo + ntiles - tile0);
+        const int count = min(QUARTER_TILES, ntiles - tile0);
         for (int e = threadIdx.x; e < count * 4; e += THREADS) {
-            const int kpos0 = (tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
+            const int kpos0 = tile_of(tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
             long long base = -1;
-            if (kpos0 <= pos_hi && kpos0 + 15 >= first) {
+            if (kpos0 <= pos_hi && (kpos0 + 15 >= first || kpos0 < p.keep_first)) {
                 const int page = table[kpos0 / p.page_size];
                 if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
                 else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
@@ -697,18 +724,19 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
             quarter_base[e] = base;
         }
     };
-    fill_quarters(tile_lo);
+    fill_quarters(0);
     __syncthreads();
 
-    auto load_tile = [&](int kt, int stage) {
+    auto load_tile = [&](int it, int stage) {                     // `it` in walking order
         unsigned char* ks = smem + stage * PL::STAGE_BYTES;
         unsigned char* vs = ks + PL::TILE_BYTES;
-        const long long* qb = quarter_base + (kt - quarter_tile0) * 4;
+        const long long* qb = quarter_base + (it - quarter_tile0) * 4;
+        const int kt = tile_of(it);
         for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += THREADS) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = kt * TILE_KEYS + row;
             const long long base = qb[row >> 4];
-            const bool valid = kpos >= first && kpos <= pos_hi && base >= 0;
+            const bool valid = (kpos >= first || kpos < p.keep_first) && kpos <= pos_hi && base >= 0;
             const long long off = valid ? base + (long long)(row & 15) * HD + chunk * 8 : 0;
             cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
             cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
@@ -722,7 +750,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
 
 #pragma unroll
     for (int s = 0; s < PL::STAGES - 1; ++s) {
-        if (s < ntiles) load_tile(tile_lo + s, s);
+        if (s < ntiles) load_tile(s, s);
         cp_async_commit();
     }
     for (int it = 0; it < ntiles; ++it) {
@@ -731,19 +759,19 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
         {
             const int nxt = it + PL::STAGES - 1;
             if (nxt < ntiles && nxt % QUARTER_TILES == 0) {
-                fill_quarters(tile_lo + nxt);
+                fill_quarters(nxt);
                 __syncthreads();
             }
-            if (nxt < ntiles) load_tile(tile_lo + nxt, nxt % PL::STAGES);
+            if (nxt < ntiles) load_tile(nxt, nxt % PL::STAGES);
             cp_async_commit();
         }
         const unsigned char* ks = smem + (it % PL::STAGES) * PL::STAGE_BYTES;
         const unsigned char* vs = ks + PL::TILE_BYTES;
-        const int key_base = (tile_lo + it) * TILE_KEYS;
-        // this warp's rows see keys up to qp1 (or qp0): skip a key tile that lies wholly behind or before them
+        const int key_base = tile_of(it) * TILE_KEYS;
+        // this warp's rows see keys up to qp1 (or qp0): skip a key tile that lies wholly behind or before them (kept first keys are never before them)
         const int warp_hi = pos_lo + min(count - 1, warp * 16 + 15), warp_lo = pos_lo + warp * 16;
-        const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
-        if (warp * 16 >= count || key_base > warp_hi || key_base + TILE_KEYS - 1 < warp_first) continue;
+        const int warp_first = first_of(warp_lo);
+        if (warp * 16 >= count || key_base > warp_hi || (key_base + TILE_KEYS - 1 < warp_first && key_base >= p.keep_first)) continue;
 
         float s[8][4];
 #pragma unroll
@@ -761,16 +789,23 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
         }
         // Scores stay unscaled here; the scale goes into the exponent's multiply-add.  Only a tile that crosses the
         // diagonal, the window's far edge or the end of the portion needs the per-element limits.
-        const bool limits = key_base + TILE_KEYS - 1 > warp_lo || warp * 16 + 15 >= count ||
-                            (p.window > 0 && key_base <= warp_lo + 15 - p.window);
+        if (p.softcap > 0.f) {
+            const float pre = p.scale / p.softcap;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = p.softcap * tanh_by_exp(s[j][e] * pre);
+        }
+        const bool limits = key_base + TILE_KEYS - 1 > warp_lo || warp * 16 + 15 >= count || key_base < first_of(warp_lo + 15);
         if (limits) {
+            const int f0 = first_of(qp0), f1 = first_of(qp1);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
                     const int qp = e < 2 ? qp0 : qp1;
-                    const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (p.window <= 0 || kpos > qp - p.window);
+                    const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (kpos >= (e < 2 ? f0 : f1) || kpos < p.keep_first);
                     if (!ok) s[j][e] = -INFINITY;
                 }
         }
@@ -833,10 +868,15 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = norm_with_sink(m0, l0, p.sink2), i1 = norm_with_sink(m1, l1, p.sink2);
+    const float i0 = norm_with_sink(m0, l0, sink2) * p.out_scale, i1 = norm_with_sink(m1, l1, sink2) * p.out_scale;
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
         const int d = i * 8 + 2 * tig;
+        if (p.out_f32) {
+            if (v0) *reinterpret_cast<float2*>(p.out_f32 + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][0] * i0, acc[i][1] * i0);
+            if (v1) *reinterpret_cast<float2*>(p.out_f32 + (size_t)(t0 + r1) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][2] * i1, acc[i][3] * i1);
+            continue;
+        }
         if (v0) *reinterpret_cast<uint32_t*>(p.out + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = pack_bf16(acc[i][0] * i0, acc[i][1] * i0);
         if (v1) *reinterpret_cast<uint32_t*>(p.out + (size_t)(t0 + r1) * p.ldo + (size_t)h * HD + d) = pack_bf16(acc[i][2] * i1, acc[i][3] * i1);
     }
@@ -950,4 +990,35 @@ EG_API int eg_attention_prefill_sink(cudaStream_t stream, const void* q, int ldq
                                      float scale, int* status, float sink_logit) {
     return attention_prefill_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo, num_heads, num_kv_heads,
                                  head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, sink_logit * 1.4426950408889634f);
+}
+
+// Prompt portions in tiles, with the further masks and score functions of PrefillParams: chunk (keys of the query's own block
+// of that many positions), keep_first (the first keys stay visible), softcap, sinks (float32 [num_heads], natural-log logits,
+// or null), maps (query row head * maps + map reads key head (head / group) * maps + map; num_heads and num_kv_heads count
+// rows and key heads, both planes hold num_kv_heads heads), out_scale; out_dtype EG_BF16, or EG_F32 for float32 rows.
+EG_API int eg_attention_prefill_masked(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table,
+                                       int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int out_dtype, int ldo,
+                                       int num_heads, int num_kv_heads, int maps, int head_dim, int page_size, long long page_stride, long long head_stride,
+                                       int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale,
+                                       int* status) {
+    if (num_tiles <= 0) return 0;
+    if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || num_heads > 65535 || maps < 1 || num_kv_heads % maps || chunk < 0 || keep_first < 0 ||
+        softcap < 0.f)
+        return (int)cudaErrorInvalidValue;
+    PrefillParams p{(const bf16*)q, ldq, (const bf16*)k_cache, (const bf16*)v_cache, page_stride, head_stride, block_table,
+                    table_stride, positions, tiles, (bf16*)out, ldo, num_heads, num_kv_heads, page_size, num_pages, window,
+                    scale, status};
+    p.chunk = chunk;
+    p.keep_first = (window > 0 || chunk > 0) ? keep_first : 0;
+    p.maps = maps;
+    p.softcap = softcap;
+    p.sinks = sinks;
+    p.out_scale = out_scale;
+    if (out_dtype == EG_F32) p.out_f32 = (float*)out;
+    switch (head_dim) {
+        case 32: return launch_prefill<32>(stream, p, num_tiles);
+        case 64: return launch_prefill<64>(stream, p, num_tiles);
+        case 128: return launch_prefill<128>(stream, p, num_tiles);
+        default: return (int)cudaErrorInvalidValue;
+    }
 }

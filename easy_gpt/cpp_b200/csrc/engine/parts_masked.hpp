@@ -19,8 +19,10 @@ namespace easygpt::engine {
 // with maps = 2 and lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (tensors .lq1 .lk1 .lq2 .lk2 [dim]):
 // o = a_1 - lambda a_2, divided by its root mean square over vdim (norm_eps) and multiplied by (1 - diff);
 // out = W_o (heads' outputs side by side, times out_scale).  The cache keeps one row (keys | value) per token and key head;
-// where maps = 1 and dim = vdim it keeps keys and values in planes of their own.  With a window or a chunk the cache manager
-// gives pages back that no coming token can see, except those of the kept first positions.
+// where dim = vdim it keeps keys and values in planes of their own with a head per (key head, map), the value stored once per
+// map: G * maps ordinary key/value heads, which in bfloat16 (heads of 32, 64 or 128) the tiled tensor-core kernel walks, for
+// prompt portions and, as tiles of one token, for single tokens; everything else runs on the generic kernel.  With a window
+// or a chunk the cache manager gives pages back that no coming token can see, except those of the kept first positions.
 // Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, maps, window, chunk, keep_first, softcap, sinks, qk_norm,
 // norm_eps, diff, out_scale.  Tensors: .q .k .v .o (+ .q.norm .k.norm, .sink, .lq1 .lk1 .lq2 .lk2).
 class MaskedAttention : public Mixer {
@@ -83,15 +85,15 @@ public:
         return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * maps_ * (dk_ + dv_) * 4 + (size_t)heads_ * dv_ * 4 + (size_t)hidden_ * 4) + (1u << 16);
     }
     bool capturable() const override { return true; }
-    // keys and values in planes of their own where a head has one key of the value's size, else side by side in one row
-    bool planes() const { return maps_ == 1 && dk_ == dv_; }
+    // keys and values in planes of their own where they have one size (a head per map), else side by side in one row
+    bool planes() const { return dk_ == dv_; }
     // the cache may let go of what no coming token sees: the window, or (a chunk never reaches further back than its size) the chunk
     long long kept_back() const {
         if (window_ > 0 && chunk_ > 0) return std::min(window_, chunk_);
         return window_ > 0 ? window_ : chunk_ > 0 ? chunk_ : -1;
     }
     CacheNeed cache_need() const override {
-        const CacheNeed n = planes() ? CacheNeed::paged(kv_heads_, dk_, kept_back()) : CacheNeed::paged_joint(kv_heads_, maps_ * dk_, dv_, kept_back());
+        const CacheNeed n = planes() ? CacheNeed::paged(kv_heads_ * maps_, dk_, kept_back()) : CacheNeed::paged_joint(kv_heads_, maps_ * dk_, dv_, kept_back());
         return n.keeping_first(keep_first_);
     }
 
@@ -116,23 +118,35 @@ public:
                                                  tables.slot_map, cache.writes ? cache.k : nullptr, values, row_stride, cache.head_stride, cache.page_size,
                                                  cache.page_stride, (long long)cache.num_pages * cache.page_size, q.p, T, heads_, kv_heads_, maps_, dk_, dv_,
                                                  norm_kind_ == "none" ? -1.f : norm_eps_, norm_kind_ == "gain" ? q_gain_.as<float>() : nullptr,
-                                                 norm_kind_ == "gain" ? k_gain_.as<float>() : nullptr, ctx.status), "masked_attention_prepare");
+                                                 norm_kind_ == "gain" ? k_gain_.as<float>() : nullptr, planes() ? 1 : 0, ctx.status), "masked_attention_prepare");
         Rows attn{ctx.take_rows(T, heads_ * dv_, dtype), dtype, T, heads_ * dv_, heads_ * dv_};
-        if (maps_ == 1) {
-            launch_check(eg_masked_attention(ctx.stream, (int)dtype, q.p, cache.k, values, row_stride, cache.head_stride, tables.block_table, tables.table_width,
-                                             ctx.token_seq, ctx.positions, nullptr, attn.p, (int)dtype, attn.ld, T, heads_, kv_heads_, 1, dk_, dv_, cache.page_size,
-                                             cache.page_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_,
-                                             sinks_ ? sink_.as<float>() : nullptr, out_scale_, ctx.status), "masked_attention");
+        // one map: the heads' outputs at once; two: both maps of every head in float32, then their difference, its norm and its
+        // factor in one kernel
+        float* both = maps_ == 2 ? ctx.take<float>((size_t)T * rows * dv_) : nullptr;
+        void* out = both ? (void*)both : attn.p;
+        const DType out_dtype = both ? DType::F32 : dtype;
+        const long long ldo = both ? (long long)rows * dv_ : attn.ld;
+        const float* sinks = sinks_ ? sink_.as<float>() : nullptr;
+        const float factor = both ? 1.0f : out_scale_;
+        if (dtype == DType::BF16 && planes() && (dk_ == 32 || dk_ == 64 || dk_ == 128) && cache.page_size % 16 == 0) {
+            auto tiled = [&](const int* tiles, int count) {
+                launch_check(eg_attention_prefill_masked(ctx.stream, q.p, (int)q.ld, cache.k, cache.v, tables.block_table, tables.table_width, ctx.positions, tiles,
+                                                         count, out, (int)out_dtype, (int)ldo, rows, kv_heads_ * maps_, maps_, dk_, cache.page_size, cache.page_stride,
+                                                         cache.head_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_, sinks,
+                                                         factor, ctx.status), "attention_prefill_masked");
+            };
+            if (ctx.query_tiles) tiled(ctx.query_tiles, ctx.num_tiles);
+            const int singles = ctx.query_tiles ? ctx.num_small : T;
+            if (singles > 0) tiled(single_token_tiles(ctx, ctx.query_tiles ? ctx.small_tokens : nullptr, singles), singles);
         } else {
-            // both maps of every head in float32, then their difference, its norm and its factor in one kernel
-            float* both = ctx.take<float>((size_t)T * rows * dv_);
             launch_check(eg_masked_attention(ctx.stream, (int)dtype, q.p, cache.k, values, row_stride, cache.head_stride, tables.block_table, tables.table_width,
-                                             ctx.token_seq, ctx.positions, nullptr, both, (int)DType::F32, (long long)rows * dv_, T, heads_, kv_heads_, 2, dk_, dv_,
-                                             cache.page_size, cache.page_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_,
-                                             nullptr, 1.0f, ctx.status), "masked_attention");
+                                             ctx.token_seq, ctx.positions, nullptr, out, (int)out_dtype, ldo, T, heads_, kv_heads_, maps_, dk_, dv_, cache.page_size,
+                                             cache.page_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_, sinks, factor,
+                                             planes() ? 1 : 0, ctx.status), "masked_attention");
+        }
+        if (both)
             launch_check(eg_attention_map_difference(ctx.stream, both, attn.p, (int)dtype, attn.ld, T, heads_, dv_, lambda_, norm_eps_,
                                                      (float)(1.0 - diff_) * out_scale_), "attention_map_difference");
-        }
         const Rows o = out_(ctx, attn, /*out_f32=*/true);
         Delta d;
         d.p = o.p;
@@ -141,6 +155,18 @@ public:
     }
 
 private:
+    // the step's single tokens (those of `list`, or all) as tiles of one token for the tiled kernel: made by the first layer
+    // that asks and shared by the step's other layers
+    static const int* single_token_tiles(const StepContext& ctx, const int* list, int count) {
+        auto& shared = const_cast<StepContext&>(ctx).shared;
+        auto it = shared.find("single token tiles");
+        if (it != shared.end()) return (const int*)it->second;
+        int* tiles = ctx.take_for_step<int>((size_t)3 * count);
+        launch_check(eg_single_token_tiles(ctx.stream, list, ctx.token_seq, tiles, count), "single_token_tiles");
+        shared["single token tiles"] = tiles;
+        return tiles;
+    }
+
     int hidden_, heads_, kv_heads_, dk_, dv_, maps_;
     float scale_;
     long long window_, chunk_, keep_first_;

@@ -73,6 +73,10 @@ def model(layers, width=64, vocab=131, eps=1e-5, embedding_scale=0.7, limit=2.5)
 GENERAL = model([(two_maps(), 96), (side(), 80), (chunked(heads=3, kv_heads=1, dim=8, vdim=8, scale=0.5, size=33, rot_dims=8), None), ("same", 1), ("same", 0),
                  (side(left=(2, 1, 24, 8, 0.2), right=(2, 2, 24, 8, 3), size=9, keep_first=11, softcap=None), 48)])
 GENERAL_RANKS = {1: (5, 12), 5: 3}
+# keys and values of one size (32, 64, 128): in bfloat16 the attention then runs on the tiled tensor-core kernel, prompt portions and single tokens alike
+TENSOR = model([(two_maps(heads=4, kv_heads=2, dim=32, vdim=32, size=20, rot_dims=16), 96), (side(left=(4, 2, 64, 64, 0.2), right=(2, 1, 32, 64, 4), size=24, keep_first=5), 80),
+                (chunked(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, size=33, rot_dims=64), None), ("same", 1), ("same", 0)], width=128)
+BOTH = {"general": GENERAL, "tensor": TENSOR}
 # widths that leave the decode product's alignment rule, head sizes that are no powers of two, two taps, a rotation over part of an odd-sized head
 ODD = model([(side(left=(3, 3, 12, 10, 0.4), right=(3, 1, 20, 10, 2), size=7, keep_first=3), 52), (chunked(heads=3, kv_heads=3, dim=12, vdim=10, scale=0.4, size=7, rot_dims=6, base=300.0), 36),
              (two_maps(heads=3, kv_heads=1, dim=10, vdim=6, scale=0.4, size=9, rot_dims=10, diff=0.2), None)], width=72, vocab=77, embedding_scale=None)
@@ -94,6 +98,10 @@ ALONE = {
     "two_maps_all_keys": model([(two_maps(size=None, rot_dims=None), None)]),
     "two_maps_wide": model([(two_maps(heads=6, kv_heads=3, dim=64, vdim=128, scale=0.11, size=40, rot_dims=16, diff=0.8), None)], width=128),
     "two_maps_equal_sizes": model([(two_maps(heads=2, kv_heads=2, dim=32, vdim=32, scale=0.2, size=17, rot_dims=32, diff=0.1), None)]),
+    "two_maps_planes_64": model([(two_maps(heads=6, kv_heads=2, dim=64, vdim=64, scale=0.12, size=70, rot_dims=24, diff=0.45), None)], width=128),
+    "two_maps_planes_128": model([(two_maps(heads=2, kv_heads=1, dim=128, vdim=128, scale=0.09, size=None, rot_dims=64, diff=0.3), None)], width=128),
+    "side_planes_128": model([(side(left=(2, 1, 128, 128, 0.09), right=(2, 2, 64, 64, 3), size=65, keep_first=70, softcap=4.0), None)], width=128),
+    "side_planes_32": model([(side(left=(6, 3, 32, 32, 0.2), right=(2, 1, 16, 16, 2), size=33, keep_first=1, softcap=None), 64)]),
     "side": model([(side(), None)]),
     "side_all_keys": model([(side(size=None, keep_first=None), None)]),
     "side_no_first": model([(side(keep_first=None), None)]),
@@ -107,7 +115,7 @@ ALONE = {
     "feed_forward": model([(chunked(heads=2, kv_heads=2, dim=8, vdim=8), 100)], limit=0.6),
     "shared_tensors": model([(side(), 40), (two_maps(), None), ("same", 0), ("same", 1), ("same", 2)]),
 }
-RANKS = {"general": GENERAL_RANKS, "ones": ONES_RANKS, "side_wide": {0: (24, 40)}, "side": {0: (16, 7)}}
+RANKS = {"general": GENERAL_RANKS, "ones": ONES_RANKS, "side_wide": {0: (24, 40)}, "side": {0: (16, 7)}, "tensor": {1: (9, 16)}}
 
 
 def tokens(vocab, n, seed):
@@ -167,7 +175,8 @@ def test_the_restatement_itself():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,cfg", [("general", GENERAL), ("odd", ODD), ("ones", ONES), ("alone_chunked_wide", None), ("alone_two_maps_wide", None),
                                       ("alone_side_wide", None), ("alone_side_long_keys", None), ("alone_side_many_values", None), ("alone_chunked_planes", None),
-                                      ("alone_side_first_longer_than_window", None), ("alone_odd_width", None), ("alone_shared_tensors", None)])
+                                      ("alone_side_first_longer_than_window", None), ("alone_odd_width", None), ("alone_shared_tensors", None), ("tensor", TENSOR),
+                                      ("alone_two_maps_planes_64", None), ("alone_two_maps_planes_128", None), ("alone_side_planes_128", None), ("alone_side_planes_32", None)])
 def test_prompt_whole_and_token_by_token(folders, name, cfg, dtype):
     if cfg is None:
         name = name[len("alone_"):]
@@ -184,10 +193,11 @@ def test_prompt_whole_and_token_by_token(folders, name, cfg, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cuts", [[2] * 20, [3, 1, 2, 17, 1, 1, 30, 5, 2, 2, 16, 15, 1, 33], [16, 16, 16, 16, 1, 15, 48], [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12]])
-def test_portions(folders, cuts, dtype):
+@pytest.mark.parametrize("which", sorted(BOTH))
+def test_portions(folders, cuts, dtype, which):
     """Portions down to two tokens, shorter than the convolution's reach, than the windows, the chunks and the kept first tokens,
     ending on and beside page borders."""
-    folder, cfg, w = folders("general", GENERAL, seed=5)
+    folder, cfg, w = folders(which, BOTH[which], seed=5)
     toks = tokens(cfg["vocab"], sum(cuts), 7)
     want = pm.forward(cfg, w, toks)
     r = runner(folder, dtype, page_size=16)
@@ -199,9 +209,10 @@ def test_portions(folders, cuts, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_batches_of_unequal_requests(folders, dtype):
+@pytest.mark.parametrize("which", sorted(BOTH))
+def test_batches_of_unequal_requests(folders, dtype, which):
     """Four requests of different lengths advance together, portions beside single tokens; each must come out as alone."""
-    folder, cfg, w = folders("general", GENERAL, seed=5)
+    folder, cfg, w = folders(which, BOTH[which], seed=5)
     lengths = {"a": 61, "b": 9, "c": 130, "d": 33}
     toks = {k: tokens(cfg["vocab"], n, 10 + i) for i, (k, n) in enumerate(lengths.items())}
     want = {k: pm.forward(cfg, w, v) for k, v in toks.items()}
@@ -230,10 +241,11 @@ def test_batches_of_unequal_requests(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_pages_and_slots_are_used_again(folders, dtype):
+@pytest.mark.parametrize("which", sorted(BOTH))
+def test_pages_and_slots_are_used_again(folders, dtype, which):
     """Two slots and a pool of four pages: every request takes a slot (convolution inputs, delta states) and pages that
     another one has left full."""
-    folder, cfg, w = folders("general", GENERAL, seed=5)
+    folder, cfg, w = folders(which, BOTH[which], seed=5)
     r = runner(folder, dtype, pool_tokens=64, page_size=16, slots=2)
     for i in range(6):
         a, b = tokens(cfg["vocab"], 20 + i, 40 + i), tokens(cfg["vocab"], 31 - i, 60 + i)
@@ -326,8 +338,9 @@ def with_chunks_moved(by, cfg, w, toks):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("offset", ["inside", "outside"])
 @pytest.mark.parametrize("how", ["prompt", "decoded"])
+@pytest.mark.parametrize("dim", [16, 64])
 @pytest.mark.parametrize("edge", sorted(EDGES))
-def test_mask_edges(folders, dtype, offset, how, edge, dim=16):
+def test_mask_edges(folders, dtype, offset, how, edge, dim):
     """The one key that the last token looks for lies on the last position its mask still holds, or on the first it does not:
     a window's far end, a chunk's first position and the one before it, the last kept first token and the one behind it.
     The restatement with the mask moved by one gives other logits at that place (checked), so a mask that is one off shows."""
@@ -358,13 +371,15 @@ def test_mask_edges(folders, dtype, offset, how, edge, dim=16):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_far_keys_sinks_and_slow_states(folders, dtype):
+@pytest.mark.parametrize("dim", [16, 64])
+def test_far_keys_sinks_and_slow_states(folders, dtype, dim):
     """Sharp attention over many pages: one kept first token far back that the last tokens look for beside a short window,
     delta states that hardly decay, a chunk of 256 positions, then decoding; and checks that the far key, the sinks, the soft
     cap and the second map matter."""
-    cfg, over = aimed(model([(side(size=12, keep_first=16, softcap=9.0), 64), (chunked(size=256, rot_dims=4), None), (two_maps(size=300), 32), ("same", 0)], vocab=140),
-                      9, 138, 139)
-    folder, cfg, w = folders("pointed", cfg, seed=9, overrides=over)
+    left = (4, 2, dim, dim + 8 if dim == 16 else dim, 0.3)                    # heads of 64 and 64: the tiled tensor-core kernel in bfloat16
+    cfg, over = aimed(model([(side(left=left, size=12, keep_first=16, softcap=9.0), 64), (chunked(dim=dim, vdim=dim, size=256, rot_dims=4), None),
+                             (two_maps(dim=dim * 2, vdim=dim * 2 if dim == 64 else 24, size=300), 32), ("same", 0)], vocab=140, width=128 if dim == 64 else 64), 9, 138, 139)
+    folder, cfg, w = folders(f"pointed{dim}", cfg, seed=9, overrides=over)
     toks = tokens(130, 400, 21)
     toks[15] = 139                                                # the key: the last kept position, at a page's border
     toks[350] = toks[395] = 138                                   # looked for in the prompt's tail and again while decoding
@@ -393,8 +408,9 @@ def test_far_keys_sinks_and_slow_states(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding_through_captured_steps(folders, dtype):
-    folder, cfg, w = folders("odd", ODD, seed=5)
+@pytest.mark.parametrize("which", ["odd", "tensor"])
+def test_long_decoding_through_captured_steps(folders, dtype, which):
+    folder, cfg, w = folders(which, ODD if which == "odd" else TENSOR, seed=5)
     toks = tokens(cfg["vocab"], 240, 31)
     want = pm.forward(cfg, w, toks)
     r = runner(folder, dtype, pool_tokens=512)
