@@ -377,7 +377,7 @@ def test_far_keys_sinks_and_slow_states(folders, dtype, dim):
     delta states that hardly decay, a chunk of 256 positions, then decoding; and checks that the far key, the sinks, the soft
     cap and the second map matter."""
     left = (4, 2, dim, dim + 8 if dim == 16 else dim, 0.3)                    # heads of 64 and 64: the tiled tensor-core kernel in bfloat16
-    cfg, over = aimed(model([(side(left=left, size=12, keep_first=16, softcap=9.0), 64), (chunked(dim=dim, vdim=dim, size=256, rot_dims=4), None),
+    cfg, over = aimed(model([(side(left=left, size=12, keep_first=16, softcap=6.0), 64), (chunked(dim=dim, vdim=dim, size=256, rot_dims=4), None),
                              (two_maps(dim=dim * 2, vdim=dim * 2 if dim == 64 else 24, size=300), 32), ("same", 0)], vocab=140, width=128 if dim == 64 else 64), 9, 138, 139)
     folder, cfg, w = folders(f"pointed{dim}", cfg, seed=9, overrides=over)
     toks = tokens(130, 400, 21)
