@@ -266,22 +266,3 @@ EG_API int eg_attention_map_difference(cudaStream_t stream, const float* maps, v
     else map_difference_kernel<float><<<blocks, 128, 0, stream>>>(maps, (float*)out, ldo, tokens, heads, dv, lambda, eps, post);
     return eg_launch_status();
 }
-
-namespace {
-__global__ void single_token_tiles_kernel(const int* __restrict__ token_list, const int* __restrict__ token_seq, int* __restrict__ tiles, int n) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int t = token_list ? token_list[i] : i;
-    tiles[3 * i] = token_seq[t];
-    tiles[3 * i + 1] = t;
-    tiles[3 * i + 2] = 1;
-}
-}  // namespace
-
-// tiles int32 [n, 3] = (block table row, token, 1) for the tokens of token_list (or tokens 0 .. n - 1): single tokens in the form
-// in which the tiled attention kernels take prompt portions
-EG_API int eg_single_token_tiles(cudaStream_t stream, const int* token_list, const int* token_seq, int* tiles, int n) {
-    if (n <= 0) return 0;
-    single_token_tiles_kernel<<<(n + 127) / 128, 128, 0, stream>>>(token_list, token_seq, tiles, n);
-    return eg_launch_status();
-}

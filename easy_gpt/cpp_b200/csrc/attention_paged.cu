@@ -52,6 +52,12 @@ struct Layout {
     }
 };
 
+// tanh by one exponent and one division: absolute error about 1e-7, which a score that goes into an exponent next can bear
+__device__ __forceinline__ float tanh_by_exp(float x) {
+    const float e = __expf(2.0f * fminf(x, 15.0f));
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
+
 struct Params {
     const bf16* q;
     int ldq;
@@ -78,6 +84,15 @@ struct Params {
     const int* token_list;        // optional: the tokens this launch works on (blockIdx.x indexes it); null: all, in order
     int cluster_merge;            // the splits of a (token, KV head) are one cluster and are merged in its first CTA's shared memory
     float sink2 = -INFINITY;      // a sink's logit times log2(e): one more term of the softmax's denominator; -inf: none
+    // Further masks and score functions (all off by default; PrefillParams has the same).  chunk: a query sees keys of its own
+    // block of `chunk` positions only; keep_first: keys 0 .. keep_first - 1 stay visible whatever window and chunk say (their
+    // key tiles are walked first); softcap c: the scaled score becomes c tanh(score / c); sinks: a logit per query row
+    // (natural log) in place of sink2; maps m: query rows head * m + map read key head (head / group) * m + map (both planes
+    // hold num_kv_heads heads; num_heads counts rows); out_scale: a factor on the output; out_f32: float32 output [tokens, ldo].
+    int chunk = 0, keep_first = 0, maps = 1;
+    float softcap = 0.f, out_scale = 1.f;
+    const float* sinks = nullptr;
+    float* out_f32 = nullptr;
 };
 
 // acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
@@ -106,6 +121,10 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     const int g0 = (blockIdx.y % gblocks) * 16;                   // first query head of the group handled here
     const int split = blockIdx.z;
     const float scale_log2 = p.scale * 1.4426950408889634f;
+    const float cap_pre = p.softcap > 0.f ? p.scale / p.softcap : 0.f, cap_post = p.softcap * 1.4426950408889634f;
+    // the query row (and output row) of row r of this key head's group, and its sink (base 2)
+    auto head_of = [&](int r) { return p.maps == 1 ? kvh * G + r : ((kvh / p.maps) * G + r) * p.maps + kvh % p.maps; };
+    auto sink_of = [&](int r) { return p.sinks ? p.sinks[head_of(r)] * 1.4426950408889634f : p.sink2; };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
 
@@ -126,12 +145,19 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     if (p.use_pdl == 1) asm volatile("griddepcontrol.launch_dependents;\n" ::);
     const int pos = p.positions[t];
     const int fresh_from = p.seq_context ? p.seq_context[p.token_seq[t]] : 0;
-    const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    if (p.chunk > 0) first = max(first, pos / p.chunk * p.chunk);
     const int* table = p.block_table + (size_t)p.token_seq[t] * p.table_stride;
     const int tile_lo = first / TILE_KEYS, tile_hi = pos / TILE_KEYS;           // inclusive
-    const int per = (tile_hi - tile_lo + 1 + p.splits - 1) / p.splits;
-    const int my_lo = tile_lo + split * per;
-    const int my_hi = min(tile_hi, my_lo + per - 1);
+    // Key tiles in the order they are walked: those of the kept first keys that lie wholly in front of the others, then the
+    // tiles from the first visible key on.  my_lo, my_hi and every tile index below count in that order; tile_of gives the tile.
+    const int kept_tiles = p.keep_first > 0 ? min((p.keep_first + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
+    const int all_tiles = kept_tiles + tile_hi - tile_lo + 1;
+    auto tile_of = [&](int w) { return w < kept_tiles ? w : tile_lo + w - kept_tiles; };
+    auto visible = [&](int kpos) { return (kpos >= first || kpos < p.keep_first) && kpos <= pos; };
+    const int per = (all_tiles + p.splits - 1) / p.splits;
+    const int my_lo = split * per;
+    const int my_hi = min(all_tiles - 1, my_lo + per - 1);
     const int ntiles = my_hi - my_lo + 1;                                       // may be <= 0
 
     // Where every 16-key quarter of this CTA's tiles starts in the cache (element offset, -1: nothing to read):
@@ -142,9 +168,9 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         quarter_tile0 = tile0;
         const int count = min(QUARTER_TILES, my_hi - tile0 + 1);
         for (int e = threadIdx.x; e < count * 4; e += NT) {
-            const int kpos0 = (tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
+            const int kpos0 = tile_of(tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
             long long base = -1;
-            if (kpos0 <= pos && kpos0 + 15 >= first) {
+            if (kpos0 <= pos && (kpos0 + 15 >= first || kpos0 < p.keep_first)) {
                 const int page = table[kpos0 / p.page_size];
                 if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
                 else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
@@ -161,10 +187,10 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         const long long* qb = quarter_base + (tile - quarter_tile0) * 4;
         for (int e = threadIdx.x; e < TILE_KEYS * L::CHUNKS; e += NT) {
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
-            const int kpos = tile * TILE_KEYS + row;
+            const int kpos = tile_of(tile) * TILE_KEYS + row;
             const long long base = qb[row >> 4];
-            const bool valid = kpos >= first && kpos <= pos && base >= 0;
-            const bool fresh = kpos >= first && kpos <= pos && kpos >= fresh_from;
+            const bool valid = visible(kpos) && base >= 0;
+            const bool fresh = visible(kpos) && kpos >= fresh_from;
             if ((mode == 1 && fresh) || (mode == 2 && !fresh)) continue;
             const long long off = valid ? base + (long long)(row & 15) * HD + chunk * 8 : 0;
             cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
@@ -177,7 +203,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         for (int g = 0; g < TI; ++g) {
             const int tile = it_tile0 + g;
             if (tile > my_hi) break;
-            if (mode == 2 && (tile + 1) * TILE_KEYS <= fresh_from) continue;
+            if (mode == 2 && (tile_of(tile) + 1) * TILE_KEYS <= fresh_from) continue;
             load_one(tile, smem + stage * L::STAGE_BYTES + g * L::GROUP_BYTES, mode);
         }
     };
@@ -206,8 +232,8 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     uint32_t qf[HD / 16][4];
     {
         const int r0 = g0 + gid, r1 = g0 + gid + 8;
-        const bf16* q0 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r0) * HD;
-        const bf16* q1 = p.q + (size_t)t * p.ldq + (size_t)(kvh * G + r1) * HD;
+        const bf16* q0 = p.q + (size_t)t * p.ldq + (size_t)head_of(r0) * HD;
+        const bf16* q1 = p.q + (size_t)t * p.ldq + (size_t)head_of(r1) * HD;
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
             const int d = ks * 16 + 2 * tig;
@@ -238,8 +264,8 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         const unsigned char* ks = smem + (it % L::STAGES) * L::STAGE_BYTES + group * L::GROUP_BYTES;
         const unsigned char* vs = ks + L::TILE_BYTES;
         if (it * TI + group >= ntiles) continue;                                  // the run has no tile for this group of warps any more
-        const int key_base = (my_lo + it * TI + group) * TILE_KEYS + key0;        // this warp's KW keys
-        if (key_base > pos || key_base + KW - 1 < first) continue;                // nothing visible in them
+        const int key_base = tile_of(my_lo + it * TI + group) * TILE_KEYS + key0; // this warp's KW keys
+        if (key_base > pos || (key_base + KW - 1 < first && key_base >= p.keep_first)) continue;   // nothing visible in them
 
         // S = Q K^T for 16 rows x KW keys
         float s[2 * KB][4];
@@ -263,8 +289,8 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
-                const bool ok = kpos >= first && kpos <= pos;
-                s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+                const bool ok = visible(kpos);
+                s[j][e] = ok ? (p.softcap > 0.f ? cap_post * tanh_by_exp(s[j][e] * cap_pre) : s[j][e] * scale_log2) : -INFINITY;
                 if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
             }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
@@ -368,8 +394,11 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         }
         const int h = kvh * G + g0 + r;
         if (p.splits == 1) {
-            p.out[(size_t)t * p.ldo + (size_t)h * HD + d] =
-                __float2bfloat16_rn(p.sink2 == -INFINITY ? (l > 0.f ? a / l : 0.f) : a * norm_with_sink(m, l, p.sink2));
+            const float s2 = sink_of(g0 + r);
+            const float v = (s2 == -INFINITY ? (l > 0.f ? a / l : 0.f) : a * norm_with_sink(m, l, s2)) * p.out_scale;
+            const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + d;
+            if (p.out_f32) p.out_f32[at] = v;
+            else p.out[at] = __float2bfloat16_rn(v);
         } else if (p.cluster_merge) {
             const uint32_t at = incoming + (uint32_t)((cluster_rank * rows + r) * (HD + 2)) * 4u;
             asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(at + (uint32_t)d * 4u), "f"(a) : "memory");
@@ -409,10 +438,10 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                 const float2 lo = *reinterpret_cast<const float2*>(part + dq * 4), hi = *reinterpret_cast<const float2*>(part + dq * 4 + 2);
                 a.x += lo.x * w; a.y += lo.y * w; a.z += hi.x * w; a.w += hi.y * w;
             }
-            const float il = norm_with_sink(m, l, p.sink2);
-            const int h = kvh * G + g0 + r;
-            *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + (size_t)h * HD + dq * 4) =
-                make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
+            const float il = norm_with_sink(m, l, sink_of(g0 + r)) * p.out_scale;
+            const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + dq * 4;
+            if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
+            else *reinterpret_cast<uint2*>(p.out + at) = make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
         }
         return;
     }
@@ -466,7 +495,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                     f[s2] = w;
                     l += lp[s2] * w;
                 }
-                inv_l[threadIdx.x] = norm_with_sink(m, l, p.sink2);
+                inv_l[threadIdx.x] = norm_with_sink(m, l, sink_of(g0 + threadIdx.x)) * p.out_scale;
             }
             __syncthreads();
         }
@@ -491,9 +520,9 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                 }
         }
         const float il = inv_l[r];
-        const int h = kvh * G + g0 + r;
-        *reinterpret_cast<uint2*>(p.out + (size_t)t * p.ldo + (size_t)h * HD + dq * 4) =
-            make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
+        const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + dq * 4;
+        if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
+        else *reinterpret_cast<uint2*>(p.out + at) = make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
     }
 }
 
@@ -641,12 +670,6 @@ struct PrefillParams {
     const float* sinks = nullptr;
     float* out_f32 = nullptr;
 };
-
-// tanh by one exponent and one division: absolute error about 1e-7, which a score that goes into an exponent next can bear
-__device__ __forceinline__ float tanh_by_exp(float x) {
-    const float e = __expf(2.0f * fminf(x, 15.0f));
-    return 1.0f - __fdividef(2.0f, e + 1.0f);
-}
 
 template <int HD>
 struct PrefillLayout {
@@ -910,7 +933,8 @@ static int attention_paged_any(cudaStream_t stream, const void* q, int ldq, cons
                                const int* seq_context, void* out, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads,
                                int num_kv_heads, int head_dim, int page_size, long long page_stride, long long head_stride,
                                int num_pages, int window, float scale, int splits, int* status, const void* prefetch,
-                               long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list, float sink2) {
+                               long long prefetch_bytes, int* counters, int use_pdl, unsigned long long* trace, const int* token_list, float sink2,
+                               const Params* extras = nullptr) {
     if (tokens <= 0) return 0;
     if (page_size % 16 || num_kv_heads <= 0 || num_heads % num_kv_heads || splits < 1 || tokens > 0x7fffffff ||
         splits > MAX_SPLITS || (splits > 1 && (!partial_acc || !partial_ml || !counters || ldo % 4 || (uintptr_t)out % 8)))
@@ -920,6 +944,15 @@ static int attention_paged_any(cudaStream_t stream, const void* q, int ldq, cons
              page_size, num_pages, window, splits, scale, status, prefetch_bytes >= 16 ? prefetch : nullptr, prefetch_bytes,
              counters, use_pdl, trace, token_list};
     p.sink2 = sink2;
+    if (extras) {
+        p.chunk = extras->chunk;
+        p.keep_first = (window > 0 || extras->chunk > 0) ? extras->keep_first : 0;
+        p.maps = extras->maps;
+        p.softcap = extras->softcap;
+        p.out_scale = extras->out_scale;
+        p.sinks = extras->sinks;
+        p.out_f32 = extras->out_f32;
+    }
     switch (head_dim) {
         case 32: return launch<32>(stream, p, tokens);
         case 64: return launch<64>(stream, p, tokens);
@@ -1021,4 +1054,28 @@ EG_API int eg_attention_prefill_masked(cudaStream_t stream, const void* q, int l
         case 128: return launch_prefill<128>(stream, p, num_tiles);
         default: return (int)cudaErrorInvalidValue;
     }
+}
+
+// Single tokens split over their keys, with the further masks and score functions of Params: chunk, keep_first, softcap, sinks
+// (float32 [num_heads], natural-log logits, or null), maps (num_heads and num_kv_heads count rows and key heads; both planes
+// hold num_kv_heads heads), out_scale; out_dtype EG_BF16, or EG_F32 for float32 rows (ldo a multiple of four then too).
+EG_API int eg_attention_paged_masked(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table,
+                                     int table_stride, const int* token_seq, const int* positions, const int* seq_context, void* out, int out_dtype, int ldo,
+                                     float* partial_acc, float* partial_ml, int tokens, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size,
+                                     long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale,
+                                     float softcap, const float* sinks, float out_scale, int splits, int* status, int* counters, int use_pdl,
+                                     const int* token_list) {
+    if (maps < 1 || num_kv_heads % maps || chunk < 0 || keep_first < 0 || softcap < 0.f || (out_dtype == EG_F32 && (ldo % 4 || (uintptr_t)out % 16)))
+        return (int)cudaErrorInvalidValue;
+    Params extras{};
+    extras.chunk = chunk;
+    extras.keep_first = keep_first;
+    extras.maps = maps;
+    extras.softcap = softcap;
+    extras.out_scale = out_scale;
+    extras.sinks = sinks;
+    extras.out_f32 = out_dtype == EG_F32 ? (float*)out : nullptr;
+    return attention_paged_any(stream, q, ldq, k_cache, v_cache, block_table, table_stride, token_seq, positions, seq_context, out, ldo, partial_acc,
+                               partial_ml, tokens, num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, splits,
+                               status, nullptr, 0, counters, use_pdl, nullptr, token_list, -INFINITY, &extras);
 }

@@ -161,8 +161,8 @@ int eg_gemm_tcgen05_grouped_glu(cudaStream_t stream, const void* A, long long ld
 int eg_masked_attention_prepare(cudaStream_t stream, int dtype, const float* proj, long long ld, const float* table, int rot_dims, float magnitude, const int* slot_map, void* k_cache, void* v_cache, int row_stride, long long head_stride, int page_size, long long page_stride, long long pool_slots, void* q_out, int tokens, int heads, int kv_heads, int maps, int dk, int dv, float norm_eps, const float* q_gain, const float* k_gain, int planes, int* status);
 // attention_masked.cu
 int eg_masked_attention(cudaStream_t stream, int dtype, const void* q, const void* k_cache, const void* v_cache, int row_stride, long long head_stride, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* token_list, void* out, int out_dtype, long long ldo, int num_tokens, int heads, int kv_heads, int maps, int dk, int dv, int page_size, long long page_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale, int planes, int* status);
-// attention_masked.cu
-int eg_single_token_tiles(cudaStream_t stream, const int* token_list, const int* token_seq, int* tiles, int n);
+// attention_paged.cu
+int eg_attention_paged_masked(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* token_seq, const int* positions, const int* seq_context, void* out, int out_dtype, int ldo, float* partial_acc, float* partial_ml, int tokens, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale, int splits, int* status, int* counters, int use_pdl, const int* token_list);
 // attention_paged.cu
 int eg_attention_prefill_masked(cudaStream_t stream, const void* q, int ldq, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int out_dtype, int ldo, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale, int* status);
 // attention_masked.cu

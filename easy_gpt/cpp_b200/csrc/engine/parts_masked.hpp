@@ -20,8 +20,8 @@ namespace easygpt::engine {
 // o = a_1 - lambda a_2, divided by its root mean square over vdim (norm_eps) and multiplied by (1 - diff);
 // out = W_o (heads' outputs side by side, times out_scale).  The cache keeps one row (keys | value) per token and key head;
 // where dim = vdim it keeps keys and values in planes of their own with a head per (key head, map), the value stored once per
-// map: G * maps ordinary key/value heads, which in bfloat16 (heads of 32, 64 or 128) the tiled tensor-core kernel walks, for
-// prompt portions and, as tiles of one token, for single tokens; everything else runs on the generic kernel.  With a window
+// map: G * maps ordinary key/value heads, which in bfloat16 (heads of 32, 64 or 128) the engine's tensor-core kernels walk: the
+// tiled one for prompt portions, the split-key one for single tokens; everything else runs on the generic kernel.  With a window
 // or a chunk the cache manager gives pages back that no coming token can see, except those of the kept first positions.
 // Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, maps, window, chunk, keep_first, softcap, sinks, qk_norm,
 // norm_eps, diff, out_scale.  Tensors: .q .k .v .o (+ .q.norm .k.norm, .sink, .lq1 .lk1 .lq2 .lk2).
@@ -82,7 +82,9 @@ public:
     }
     size_t weight_bytes() const override { return qkv_.weight_bytes() + out_.weight_bytes(); }
     size_t arena_bytes(long long T) const override {
-        return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * maps_ * (dk_ + dv_) * 4 + (size_t)heads_ * dv_ * 4 + (size_t)hidden_ * 4) + (1u << 16);
+        // partial results of single tokens whose keys are dealt to several CTAs: bounded by the CTAs of a few waves
+        const size_t partials = planes() ? (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(dv_ + 2) * 4 : 0;
+        return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * maps_ * (dk_ + dv_) * 4 + (size_t)heads_ * dv_ * 4 + (size_t)hidden_ * 4) + partials + (1u << 16);
     }
     bool capturable() const override { return true; }
     // keys and values in planes of their own where they have one size (a head per map), else side by side in one row
@@ -135,9 +137,28 @@ public:
                                                          cache.head_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_, sinks,
                                                          factor, ctx.status), "attention_prefill_masked");
             };
+            // prompt portions in tiles of query tokens; single tokens (decoding, short entries) split over their keys
             if (ctx.query_tiles) tiled(ctx.query_tiles, ctx.num_tiles);
             const int singles = ctx.query_tiles ? ctx.num_small : T;
-            if (singles > 0) tiled(single_token_tiles(ctx, ctx.query_tiles ? ctx.small_tokens : nullptr, singles), singles);
+            if (singles > 0) {
+                const long long reach = kept_back() < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, kept_back() + keep_first_ + 255);
+                const int key_heads = kv_heads_ * maps_;
+                const int splits = plans::attention_paged_splits(singles, rows, key_heads, reach, dk_);
+                float *acc = nullptr, *ml = nullptr;
+                int* counters = nullptr;
+                if (splits > 1) {
+                    acc = ctx.take<float>((size_t)T * rows * splits * dv_);
+                    ml = ctx.take<float>((size_t)T * rows * splits * 2);
+                    if ((size_t)singles * key_heads * ((rows / key_heads + 15) / 16) > KernelScratch::ATTENTION_COUNTERS)
+                        throw DeviceError("a step has more (token, KV head) pairs than the attention's ticket counters");
+                    counters = ctx.scratch->attention_counters.as<int>();
+                }
+                launch_check(eg_attention_paged_masked(ctx.stream, q.p, (int)q.ld, cache.k, cache.v, tables.block_table, tables.table_width, ctx.token_seq,
+                                                       ctx.positions, ctx.query_tiles ? nullptr : ctx.seq_context, out, (int)out_dtype, (int)ldo, acc, ml, singles,
+                                                       rows, key_heads, maps_, dk_, cache.page_size, cache.page_stride, cache.head_stride, cache.num_pages,
+                                                       (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_, sinks, factor, splits, ctx.status, counters,
+                                                       plans::use_pdl(), ctx.query_tiles ? ctx.small_tokens : nullptr), "attention_paged_masked");
+            }
         } else {
             launch_check(eg_masked_attention(ctx.stream, (int)dtype, q.p, cache.k, values, row_stride, cache.head_stride, tables.block_table, tables.table_width,
                                              ctx.token_seq, ctx.positions, nullptr, out, (int)out_dtype, ldo, T, heads_, kv_heads_, maps_, dk_, dv_, cache.page_size,
@@ -155,18 +176,6 @@ public:
     }
 
 private:
-    // the step's single tokens (those of `list`, or all) as tiles of one token for the tiled kernel: made by the first layer
-    // that asks and shared by the step's other layers
-    static const int* single_token_tiles(const StepContext& ctx, const int* list, int count) {
-        auto& shared = const_cast<StepContext&>(ctx).shared;
-        auto it = shared.find("single token tiles");
-        if (it != shared.end()) return (const int*)it->second;
-        int* tiles = ctx.take_for_step<int>((size_t)3 * count);
-        launch_check(eg_single_token_tiles(ctx.stream, list, ctx.token_seq, tiles, count), "single_token_tiles");
-        shared["single token tiles"] = tiles;
-        return tiles;
-    }
-
     int hidden_, heads_, kv_heads_, dk_, dv_, maps_;
     float scale_;
     long long window_, chunk_, keep_first_;

@@ -407,6 +407,34 @@ def test_far_keys_sinks_and_slow_states(folders, dtype, dim):
         assert np.abs(pm.forward(c2, w2, short) - want[:64]).max() > 4 * TOL[dtype] * np.abs(want).max(), name
 
 
+def test_long_masks_over_several_ctas(folders):
+    """Masks of hundreds of positions on the tensor-core path: a single token's keys are then dealt to several CTAs, the tiles of
+    the kept first keys among them, and a prompt tile walks kept tiles, then its window's.  One kept key far back is the one
+    that the last tokens look for (sharp weights), in a portion's tail and while two requests decode side by side."""
+    cfg, over = aimed(model([(side(left=(4, 2, 64, 64, 0.3), right=(2, 1, 16, 16, 3), size=700, keep_first=70, softcap=14.0), None),
+                             (chunked(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, size=640, rot_dims=16), None),
+                             (two_maps(heads=2, kv_heads=1, dim=32, vdim=32, scale=0.2, size=800, rot_dims=8), None)], vocab=140, width=128), 9, 138, 139)
+    folder, cfg, w = folders("long_masks", cfg, seed=9, overrides=over)
+    n = 1440
+    toks = tokens(130, n, 77)
+    toks[69] = 139                                                # the last kept position
+    for place in (1290, 1399, 1439):
+        toks[place] = 138
+    want = pm.forward(cfg, w, toks)
+    changed = list(toks)
+    changed[69] = 1
+    assert np.abs(pm.forward(cfg, w, changed)[1439] - want[1439]).max() > 4 * TOL["bfloat16"] * np.abs(want).max()
+    r = runner(folder, "bfloat16", pool_tokens=4096, most_tokens=2048)
+    ask = [0, 69, 70, 639, 640, 700, 769, 770, 899]
+    rows = [r.run([("a", toks[:900], ask)]), r.run([("a", toks[900:1300], [389, 390, 399])])]
+    r.run([("b", toks[:1300], [])])                              # a second request with the same tokens decodes beside the first
+    for t in toks[1300:]:
+        out = r.run([("a", [t], [0]), ("b", [t], [0])])
+        close(out[1:], out[:1], "bfloat16", "two requests with the same tokens")
+        rows.append(out[:1])
+    close(np.concatenate(rows), np.concatenate([want[ask], want[[1289, 1290, 1299]], want[1300:]]), "bfloat16", "long masks")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("which", ["odd", "tensor"])
 def test_long_decoding_through_captured_steps(folders, dtype, which):
