@@ -179,4 +179,6 @@ int eg_clamped_glu_bias(cudaStream_t stream, const void* x, int x_dtype, long lo
 int eg_gemm_skinny_clamped_glu_bias(cudaStream_t stream, int use_pdl, const void* W, long long ldw, const float* bias, int M, int N, int K, const void* x, long long ldx, void* out, long long ldo, int row_blocks, int k_slices, int k_split, float* scratch, int* counters, int* status, float limit);
 // gemm_tcgen05.cu
 int eg_gemm_tcgen05_pair_glu_bias(cudaStream_t stream, const void* A, long long lda, const void* W, long long ldw, const float* bias, void* out, long long ldo, int M, int N, int K, int* status, float limit);
+// sandwich.cu
+int eg_rmsnorm_add_rows(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* bias, const float* gain, float eps, void* out, int out_dtype, int tokens, int hidden);
 }  // extern "C"

@@ -83,7 +83,18 @@ public:
     struct Stream {
         float *residual, *spare;
         Delta delta, delta2;
+        // `work` already holds the stream's rows in the compute dtype, for a layer whose first sub-layer reads the stream itself
+        bool rows_ahead = false;
     };
+    // whether this layer's first sub-layer reads the stream itself (no norm and no shift in front of its part)
+    bool reads_stream_first() const { return !parallel && !sublayers.front().norm && !sublayers.front().shift; }
+    // a bias that a part left for its consumer and that no consumer took: added here, by a kernel of its own
+    static void settle_bias(const StepContext& ctx, Delta& d, int T, int hidden) {
+        if (!d.bias || !d.has_delta()) return;
+        if (d.dtype != DType::F32) throw DeviceError("a bias left to the consumer goes with a float32 output");
+        launch_check(eg_add_bias_rows(ctx.stream, (float*)d.p, hidden, d.bias, T, hidden), "add_bias_rows");
+        d.bias = nullptr;
+    }
     // adds what is pending into the residual, as kernels of their own
     static void settle(const StepContext& ctx, Stream& s, long long n, bool all) {
         if (s.delta2.has_delta()) {
@@ -156,6 +167,7 @@ public:
             in.rows = Rows{rows, ctx.dtype, T, width_, width_};
             Delta d = sub.mixer ? sub.mixer->forward(ctx, in, cache, nullptr) : sub.feed_forward->forward(ctx, in, nullptr);
             if (d.has_pre()) throw DeviceError("a part returned prepared rows without having been offered the norm that follows");
+            settle_bias(ctx, d, T, width_);
             if (sub.output_norm) {
                 d.scale = sub.output_norm->plain_gain();
                 if (!d.scale) throw DeviceError("a parallel sub-layer's output norm must be a plain gain per channel");
@@ -205,11 +217,16 @@ public:
 
     // Returns the buffer that now holds the residual stream, the other one, and what the last sub-layer left still to be
     // added (its output, or the PreNormed it prepared for next_norm, the norm that runs after this block).
-    Stream forward(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, void* work2, const Norm* next_norm) const {
+    // next_reads_stream: the layer that runs next starts with a sub-layer that reads the stream itself; a last sub-layer that
+    // joins the stream through its norm may then leave the stream's rows in `work` for it (Stream::rows_ahead).
+    Stream forward(StepContext& ctx, StepArenas& arenas, int* turn, Stream s, const CacheView& cache, void* work, void* work2, const Norm* next_norm,
+                   bool next_reads_stream = false) const {
         const int T = ctx.num_tokens;
+        const bool rows_ahead = s.rows_ahead;
+        s.rows_ahead = false;
         if (parallel) return forward_parallel(ctx, arenas, turn, s, cache, work, work2);
         settle(ctx, s, (long long)T * width_, false);
-        bool normed_ahead = false;          // `work` already holds the rows of the coming sub-layer's norm
+        bool normed_ahead = rows_ahead && reads_stream_first();          // `work` already holds the rows that the coming sub-layer reads
         for (size_t i = 0; i < sublayers.size(); ++i) {
             const SubLayer& sub = sublayers[i];
             // this sub-layer's arena: what the sub-layer before the last one left there is dead by now
@@ -233,6 +250,7 @@ public:
                 if (accepts) in.pending = &pending;
                 else in.rows = pending.materialize();
                 s.delta = sub.mixer ? sub.mixer->forward(ctx, in, cache, offer) : sub.feed_forward->forward(ctx, in, offer);
+                settle_bias(ctx, s.delta, T, hidden);
                 if (!pending.consumed) throw DeviceError("a part that accepts a pending norm must use it");
                 s.residual = pending.residual_after;
                 s.spare = pending.spare_after;
@@ -272,6 +290,20 @@ public:
                 // the branch's output goes into the stream through its norm, in float32, in one kernel; where the next sub-layer
                 // starts with a plain norm of the same stream (no shift), that norm's rows come out of the same kernel
                 const SubLayer* next = i + 1 < sublayers.size() ? &sublayers[i + 1] : nullptr;
+                // a bias that the part left, and the stream's rows for a next branch (of this layer or of the next) that reads the
+                // stream itself, ride in the same kernel
+                const bool next_reads = next ? (!next->norm && !next->shift) : next_reads_stream;
+                static const bool fuse_rows = !(std::getenv("EASY_GPT_FUSE_ROWS") && std::atoi(std::getenv("EASY_GPT_FUSE_ROWS")) == 0);     // for measurements
+                // (measured on B200 at a width of 2,048: a prompt of 2,048 tokens takes 2.69 ms with it and 2.77 without; a step of 8
+                // single tokens, where a row is one warp's chain of loads, 0.57 ms with it and 0.52 without: so for larger steps only)
+                if (fuse_rows && (d.bias || (next_reads && T > plans::SKINNY_MAX_TOKENS)) &&
+                    sub.output_norm->add_normed_rows(ctx, s.residual, d.p, d.dtype, d.bias, T, next_reads ? work : nullptr, ctx.dtype)) {
+                    if (next_reads && next) normed_ahead = true;
+                    if (next_reads && !next) s.rows_ahead = true;
+                    s.delta = Delta();
+                    continue;
+                }
+                settle_bias(ctx, d, T, hidden);
                 if (next && next->norm && next->placement == "pre" && !next->shift && !next->plain_pre_norm &&
                     sub.output_norm->add_normed_then(ctx, s.residual, d.p, d.dtype, T, next->norm.get(), work, ctx.dtype)) {
                     normed_ahead = true;
@@ -283,6 +315,7 @@ public:
                     continue;
                 }
             }
+            settle_bias(ctx, d, T, hidden);
             if (sub.output_norm) {
                 // norm(delta) in the compute dtype: through the float32 spare buffer
                 launch_check(eg_convert_rows(ctx.stream, d.p, (int)d.dtype, s.spare, (int)DType::F32, n), "convert");
@@ -527,7 +560,8 @@ public:
             }
             // the norm that the next entry starts with, unless something is added to the stream before it
             const Norm* next_norm = (i + 1 < order.size()) ? (order[i + 1].stream_add >= 0 ? nullptr : blocks[order[i + 1].layer]->first_norm()) : final_norm.get();
-            s = blocks[order[i].layer]->forward(ctx, arenas, &turn, s, view(order[i].cache, order[i].writes_cache), work, work2, next_norm);
+            const bool next_reads_stream = i + 1 < order.size() && order[i + 1].stream_add < 0 && blocks[order[i + 1].layer]->reads_stream_first();
+            s = blocks[order[i].layer]->forward(ctx, arenas, &turn, s, view(order[i].cache, order[i].writes_cache), work, work2, next_norm, next_reads_stream);
         }
         ctx.arena = &arenas.step;                // the head's rows and logits live for the step
         if (num_rows <= 0) return nullptr;

@@ -216,6 +216,14 @@ public:
         return out;
     }
 
+    // The product into float32 whose bias may be left to the consumer: where the library runs it (which writes float32 without a
+    // bias) *pending_bias is set to the bias and nothing is added here; our own kernels add it themselves (*pending_bias null).
+    Rows f32_bias_pending(const StepContext& ctx, const Rows& x, const float** pending_bias) const {
+        *pending_bias = nullptr;
+        if (dtype == DType::F32 || !has_bias() || (plans::gemm_skinny_takes(dtype, x.rows, in_features) && aligned(x))) return (*this)(ctx, x, true);
+        *pending_bias = bias_f32();
+        return without_bias_f32(ctx, x);
+    }
     // the bare product into float32, for a consumer whose own kernel adds the bias
     Rows without_bias_f32(const StepContext& ctx, const Rows& x) const {
         const int M = x.rows;
@@ -275,6 +283,13 @@ public:
     }
     bool add_normed(const StepContext& ctx, float* residual, const void* y, DType y_dtype, int num_rows) const override {
         launch_check(eg_rmsnorm_add(ctx.stream, residual, y, (int)y_dtype, size_, gain_.as<float>(), eps_, num_rows, size_), "rmsnorm_add");
+        return true;
+    }
+    bool add_normed_rows(const StepContext& ctx, float* residual, const void* y, DType y_dtype, const float* bias, int num_rows, void* out,
+                         DType out_dtype) const override {
+        const int rc = eg_rmsnorm_add_rows(ctx.stream, residual, y, (int)y_dtype, size_, bias, gain_.as<float>(), eps_, out, (int)out_dtype, num_rows, size_);
+        if (rc == (int)cudaErrorInvalidValue) return false;      // a size the fused kernel does not take
+        launch_check(rc, "rmsnorm_add_rows");
         return true;
     }
     bool add_normed_then(const StepContext& ctx, float* residual, const void* y, DType y_dtype, int num_rows, const Norm* next, void* out,
@@ -774,8 +789,8 @@ public:
                 launch_check(eg_clamped_glu_bias(ctx.stream, gu.p, (int)gu.dtype, gu.ld, gate_up_.bias_f32(), act.p, (int)dtype, inter_, T, inter_, limit_),
                              "clamped_glu");
             }
-            const Rows o = down_(ctx, act, /*out_f32=*/true);
             Delta d;
+            const Rows o = down_.f32_bias_pending(ctx, act, &d.bias);
             d.p = o.p;
             d.dtype = o.dtype;
             return d;

@@ -229,6 +229,12 @@ public:
                                  void* /*out*/, DType /*out_dtype*/) const {
         return false;
     }
+    // residual[t] += this norm of (y[t] + bias) (bias float32 [size] or null), and with out also out[t] = residual[t] in out_dtype
+    // (the stream's rows for a next branch that reads the stream itself), in one kernel; false: this norm cannot
+    virtual bool add_normed_rows(const StepContext& /*ctx*/, float* /*residual*/, const void* /*y*/, DType /*y_dtype*/, const float* /*bias*/,
+                                 int /*num_rows*/, void* /*out*/, DType /*out_dtype*/) const {
+        return false;
+    }
     // the gain [size] (float32, device) if this part only multiplies every channel by a number of its own (no
     // normalisation: a layer scale on a branch's output); a branch's output can then carry the gain along to the add
     virtual const float* plain_gain() const { return nullptr; }
@@ -273,6 +279,9 @@ struct Delta {
     void* p = nullptr;
     DType dtype = DType::BF16;
     const float* scale = nullptr;       // a gain per channel (float32 [hidden]) that the add applies: x += scale * p
+    // a bias per channel (float32 [hidden]) that p (float32 then) still lacks: a consumer that reads p anyway adds it on the
+    // way (the norm on a branch's output); the block adds it by a kernel of its own before anything else reads p
+    const float* bias = nullptr;
     PreNormed pre;
     bool has_delta() const { return p != nullptr; }
     bool has_pre() const { return pre.norm != nullptr; }

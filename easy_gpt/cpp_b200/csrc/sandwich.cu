@@ -128,6 +128,51 @@ __global__ void __launch_bounds__(256) rmsnorm_add_warp_kernel(float* __restrict
     }
 }
 
+// x[t] += gain * z / rms(z) with z = y[t] + bias (bias may be null), then (out given) out[t] = x[t] in out's type: a branch joins
+// the stream through its norm, the bias of its last product on the way, and the stream's rows for a next branch that reads the
+// stream itself follow from the row in registers
+template <typename TD, typename TO, int VPL>
+__global__ void __launch_bounds__(256) rmsnorm_add_rows_warp_kernel(float* __restrict__ stream, const TD* __restrict__ y, long long ldy,
+                                                                    const float* __restrict__ bias, const float* __restrict__ gain, float eps,
+                                                                    TO* __restrict__ out, int tokens, int hidden) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const int quads = hidden / 4;
+    const TD* row = y + (size_t)t * ldy;
+    float* x = stream + (size_t)t * hidden;
+    float4 v[VPL], r[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        v[i] = q < quads ? load4(row, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        r[i] = q < quads ? load4(x, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (bias) {                                 // a loop of its own: the rows' loads above are all in flight before anything waits
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int q = i * 32 + lane;
+            if (q >= quads) continue;
+            const float4 b = load4(bias, q);
+            v[i] = make_float4(v[i].x + b.x, v[i].y + b.y, v[i].z + b.z, v[i].w + b.w);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) ss += squares(v[i]);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+        const int q = i * 32 + lane;
+        if (q >= quads) continue;
+        const float4 g = load4(gain, q);
+        r[i] = make_float4(r[i].x + g.x * (v[i].x * inv), r[i].y + g.y * (v[i].y * inv), r[i].z + g.z * (v[i].z * inv), r[i].w + g.w * (v[i].w * inv));
+        store4(x, q, r[i]);
+        if (out) store4(out + (size_t)t * hidden, q, r[i]);
+    }
+}
+
 // x[t] += gain * y[t] / rms(y[t]), then out[t] = gain2 * x[t] / rms(x[t]): a branch joins the stream through its norm and the
 // norm in front of the next branch follows from the row in registers
 template <typename TD, typename TO, int VPL>
@@ -377,6 +422,34 @@ EG_API int eg_rmsnorm_add_norm(cudaStream_t stream, float* residual, const void*
     else { EG_ADD_NORM_V(float, float); }
 #undef EG_ADD_NORM_V
 #undef EG_ADD_NORM
+    return eg_launch_status();
+}
+
+// residual[t] += gain * z / rms(z), z = y[t] + bias (bias float32 [hidden] or null); with out, also out[t] = residual[t] in
+// out_dtype, in one kernel.  Returns cudaErrorInvalidValue for sizes it does not take (rows of up to 4,096 values, a multiple
+// of 4, 16-byte aligned).
+EG_API int eg_rmsnorm_add_rows(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* bias, const float* gain, float eps,
+                               void* out, int out_dtype, int tokens, int hidden) {
+    if (tokens <= 0) return 0;
+    if (hidden % 4 || hidden > 4096 || ldy % 4 || !aligned16(residual) || !aligned16(y) || !aligned16(gain) || (bias && !aligned16(bias)) ||
+        (out && !aligned16(out)))
+        return (int)cudaErrorInvalidValue;
+    int blocks, nt;
+    warp_rows_launch(tokens, &blocks, &nt);
+    const int vpl = (hidden / 4 + 31) / 32;
+#define EG_ADD_ROWS(TD, TO, V) \
+    rmsnorm_add_rows_warp_kernel<TD, TO, V><<<blocks, nt, 0, stream>>>(residual, (const TD*)y, ldy, bias, gain, eps, (TO*)out, tokens, hidden)
+#define EG_ADD_ROWS_V(TD, TO)                  \
+    if (vpl <= 4) EG_ADD_ROWS(TD, TO, 4);      \
+    else if (vpl <= 8) EG_ADD_ROWS(TD, TO, 8); \
+    else if (vpl <= 16) EG_ADD_ROWS(TD, TO, 16); \
+    else EG_ADD_ROWS(TD, TO, 32)
+    if (y_dtype == EG_BF16 && out_dtype == EG_BF16) { EG_ADD_ROWS_V(bf16, bf16); }
+    else if (y_dtype == EG_BF16) { EG_ADD_ROWS_V(bf16, float); }
+    else if (out_dtype == EG_BF16) { EG_ADD_ROWS_V(float, bf16); }
+    else { EG_ADD_ROWS_V(float, float); }
+#undef EG_ADD_ROWS_V
+#undef EG_ADD_ROWS
     return eg_launch_status();
 }
 
