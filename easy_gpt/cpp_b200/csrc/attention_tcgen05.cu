@@ -228,7 +228,31 @@ struct Params {
     int* queue;
     int num_tiles, max_parts, part_tiles;
     int piece_rows;            // keys a TMA box of K or V holds: 64, 32 or 16, a divisor of the page size
+    // Further masks and score functions (all off by default).  chunk: a query sees keys of its own block of `chunk` positions
+    // only; keep_first: keys 0 .. keep_first - 1 stay visible whatever window and chunk say (their key tiles are walked first);
+    // softcap c: the scaled score becomes c tanh(score / c); sinks: a logit per query row (natural log) in place of sink2;
+    // maps m: query rows head * m + map read key head (head / group) * m + map (both planes hold num_kv_heads heads; num_heads
+    // counts rows); out_scale: a factor on the output; out_f32: float32 output [tokens, ldo] instead of `out`.
+    int chunk = 0, keep_first = 0, maps = 1;
+    float softcap = 0.f, out_scale = 1.f;
+    const float* sinks = nullptr;
+    float* out_f32 = nullptr;
 };
+
+// the first key that the window and the chunk of a query at `pos` leave visible (never decreasing in pos)
+__device__ __forceinline__ int first_visible(const Params& p, int pos) {
+    const int w = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    return p.chunk > 0 ? max(w, pos / p.chunk * p.chunk) : w;
+}
+// A query tile's key tiles in the order they are walked: the tiles of the kept first keys that lie wholly in front of the
+// others (this many), then the tiles from all_lo, the tile of the first visible key, on.
+__device__ __forceinline__ int kept_tiles_of(const Params& p, int all_lo) { return p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, all_lo) : 0; }
+__device__ __forceinline__ float sink_of(const Params& p, int h) { return p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2; }
+// tanh by one exponent and one division: absolute error about 1e-7, which a score that goes into an exponent next can bear
+__device__ __forceinline__ float tanh_by_exp(float x) {
+    const float e = __expf(2.0f * fminf(x, 15.0f));
+    return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
 
 // acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
 // sink's term 2^(sink2 - m) joining the sum (in a form that cannot overflow whatever m is)
@@ -305,8 +329,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const int u_tile = p.num_tiles - 1 - u / (p.max_parts * p.num_heads);
                 const int u_t0 = p.tiles[u_tile * 3 + 1], u_count = p.tiles[u_tile * 3 + 2];
                 const int u_lo = p.positions[u_t0], u_hi = u_lo + u_count - 1;
-                const int u_first = (p.window > 0 && u_lo - p.window + 1 > 0) ? u_lo - p.window + 1 : 0;
-                const int u_tiles = u_hi / BN - u_first / BN + 1;
+                const int u_first = first_visible(p, u_lo);
+                const int u_tiles = kept_tiles_of(p, u_first / BN) + u_hi / BN - u_first / BN + 1;
                 if (u % p.max_parts < min(p.max_parts, (u_tiles + p.part_tiles - 1) / p.part_tiles)) break;
             }
             unit_slot[round & 1] = u;
@@ -317,15 +341,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int part = unit % p.max_parts;
         const int h = (unit / p.max_parts) % p.num_heads;
         const int tile = p.num_tiles - 1 - unit / (p.max_parts * p.num_heads);
-        const int kvh = h / (p.num_heads / p.num_kv_heads);
+        const int kvh = (h / p.maps) / (p.num_heads / p.num_kv_heads) * p.maps + h % p.maps;
         const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
         const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;        // positions in a tile are consecutive
-        const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-        // the key tiles of this query tile, and this unit's part of them
-        const int all_lo = first / BN, all_tiles = pos_hi / BN - all_lo + 1;
+        const int first = first_visible(p, pos_lo);
+        // the key tiles of this query tile in walking order (kept tiles, then from the first visible key's), and this unit's part of them
+        const int all_lo = first / BN, kept = kept_tiles_of(p, all_lo), all_tiles = kept + pos_hi / BN - all_lo + 1;
         const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
         const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
-        const int tile_lo = all_lo + part_begin, ntiles = part_end - part_begin;
+        const int ntiles = part_end - part_begin;
+        auto tile_of = [&](int i) { const int w = part_begin + i; return w < kept ? w : all_lo + w - kept; };      // the unit's i-th key tile
         if (p.trace && threadIdx.x == 0) {                      // profiling: per unit start, end (ns), SM, key tiles
             unsigned long long now;
             unsigned smid;
@@ -355,8 +380,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // looked up 32 at a time, one by each lane, a batch ahead: the block-table entry, and from it the piece's row in
             // the cache maps.  A piece outside the visible keys reads the last page.
             auto entry_of = [&](int f) {
-                const int kpos0 = (tile_lo + f / pieces) * BN + (f % pieces) * p.piece_rows;
-                if (f / pieces >= ntiles || kpos0 > pos_hi || kpos0 + p.piece_rows - 1 < first) return p.num_pages - 1;
+                const int kpos0 = tile_of(f / pieces) * BN + (f % pieces) * p.piece_rows;
+                if (f / pieces >= ntiles || kpos0 > pos_hi || (kpos0 + p.piece_rows - 1 < first && kpos0 >= p.keep_first)) return p.num_pages - 1;
                 return __ldg(table + kpos0 / p.page_size);
             };
             auto row_of = [&](int page, int f) {
@@ -364,7 +389,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     atomicOr(p.status, EG_STATUS_BAD_PAGE);
                     page = p.num_pages - 1;
                 }
-                const int kpos0 = (tile_lo + f / pieces) * BN + (f % pieces) * p.piece_rows;
+                const int kpos0 = tile_of(f / pieces) * BN + (f % pieces) * p.piece_rows;
                 return (int)((long long)page * p.page_rows + (long long)kvh * p.head_rows + (kpos0 % p.page_size));
             };
             int rows = row_of(entry_of(lane), lane), ahead = entry_of(32 + lane);
@@ -469,9 +494,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const bool valid = row < count;
             const int qpos = pos_lo + row;
             const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
-            const int warp_first = (p.window > 0 && warp_lo - p.window + 1 > 0) ? warp_lo - p.window + 1 : 0;
+            const int warp_first = first_visible(p, warp_lo), row_first = first_visible(p, qpos);
             const bool warp_has_rows = quad * 32 < count;
-            const float scale_log2 = p.scale * 1.4426950408889634f;
+            // with a soft cap the scores are scaled and capped as they come out of TMEM; else the scale rides in the exponent
+            const float scale_log2 = p.softcap > 0.f ? 1.4426950408889634f : p.scale * 1.4426950408889634f;
+            const float cap_pre = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
             const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
             const uint32_t o_lane = lane_base + (uint32_t)(S::O_COL + g * HD);
 
@@ -487,9 +514,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (!ok) break;
                 tc_fence_after();
                 STAMP(1)
-                const int key_base = (tile_lo + j) * BN;
-                // a key tile that lies wholly behind or before this warp's rows contributes nothing
-                const bool skip = !warp_has_rows || key_base > warp_hi || key_base + BN - 1 < warp_first;
+                const int key_base = tile_of(j) * BN;
+                // a key tile that lies wholly behind or before this warp's rows contributes nothing (kept first keys are never before them)
+                const bool skip = !warp_has_rows || key_base > warp_hi || (key_base + BN - 1 < warp_first && key_base >= p.keep_first);
                 float c = 1.f, ref = 0.f;
                 float s[64];
                 if (!skip) {
@@ -506,13 +533,18 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                     STAMP(2)
                     // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
-                    const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count ||
-                                        (p.window > 0 && key_base <= warp_lo + 31 - p.window);
+                    if (p.softcap > 0.f) {
+#pragma unroll
+                        for (int e = 0; e < 64; ++e) s[e] = p.softcap * tanh_by_exp(s[e] * cap_pre);
+                    }
+                    // (also a tile with kept first keys, and one in which a chunk of some row of the warp begins)
+                    const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count || key_base < first_visible(p, warp_lo + 31) ||
+                                        key_base < p.keep_first;
                     if (limits) {
 #pragma unroll
                         for (int e = 0; e < 64; ++e) {
                             const int kpos = key_base + e;
-                            const bool see = valid && kpos <= qpos && (p.window <= 0 || kpos > qpos - p.window);
+                            const bool see = valid && kpos <= qpos && (kpos >= row_first || kpos < p.keep_first);
                             if (!see) s[e] = -INFINITY;
                         }
                     }
@@ -650,8 +682,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 // the second group's rows are with the first
             } else if (ok && parts == 1) {
                 tc_fence_after();
-                const float inv = norm_with_sink(m, l, p.sink2);
-                uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD);
+                const float inv = norm_with_sink(m, l, sink_of(p, h)) * p.out_scale;
+                const size_t at = (size_t)(t0 + row) * p.ldo + (size_t)h * HD;
+                uint4* dst = reinterpret_cast<uint4*>(p.out + at);
+                float4* dst32 = reinterpret_cast<float4*>(p.out_f32 + at);
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     float o[32];
@@ -662,7 +696,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = o[8 * ch + e] * inv;
-                            dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                            if (p.out_f32) {
+                                dst32[c0 / 4 + 2 * ch] = make_float4(v[0], v[1], v[2], v[3]);
+                                dst32[c0 / 4 + 2 * ch + 1] = make_float4(v[4], v[5], v[6], v[7]);
+                            } else {
+                                dst[c0 / 8 + ch] = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
+                            }
                         }
                     }
                 }
@@ -723,8 +762,8 @@ attention_merge_parts_kernel(const Params p) {
     const int tile = blockIdx.x, h = blockIdx.y;
     const int t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
     const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;
-    const int first = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int all_tiles = pos_hi / BN - first / BN + 1;
+    const int first = first_visible(p, pos_lo);
+    const int all_tiles = kept_tiles_of(p, first / BN) + pos_hi / BN - first / BN + 1;
     const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
     if (parts <= 1) return;
     const size_t slot0 = ((size_t)tile * p.num_heads + h) * p.max_parts;
@@ -752,7 +791,7 @@ attention_merge_parts_kernel(const Params p) {
             w[i] = ml[i].x == -INFINITY ? 0.f : exp2f(ml[i].x - big);                     // -inf: that part saw no key of this row
             total += w[i] * ml[i].y;
         }
-        const float inv = norm_with_sink(big, total, p.sink2);
+        const float inv = norm_with_sink(big, total, sink_of(p, h)) * p.out_scale;
         float acc[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) acc[e] = 0.f;
@@ -765,6 +804,12 @@ attention_merge_parts_kernel(const Params p) {
                 acc[4 * e + 2] = fmaf(w[i], v[i][e].z, acc[4 * e + 2]);
                 acc[4 * e + 3] = fmaf(w[i], v[i][e].w, acc[4 * e + 3]);
             }
+        }
+        if (p.out_f32) {
+            float4* dst32 = reinterpret_cast<float4*>(p.out_f32 + (size_t)(t0 + row) * p.ldo + (size_t)h * HD + c0);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dst32[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
+            continue;
         }
         uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)(t0 + row) * p.ldo + (size_t)h * HD + c0);
         dst[0] = make_uint4(pack2(acc[0] * inv, acc[1] * inv), pack2(acc[2] * inv, acc[3] * inv), pack2(acc[4] * inv, acc[5] * inv), pack2(acc[6] * inv, acc[7] * inv));
@@ -818,7 +863,7 @@ static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, lon
                                         const int* tiles, int num_tiles, void* out, long long ldo, int num_heads, int num_kv_heads,
                                         int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages,
                                         int window, float scale, int* status, long long* trace, int max_parts, int part_tiles, float* partial_o, float* partial_ml,
-                                        int* queue, float sink2) {
+                                        int* queue, float sink2, const Params* extras = nullptr) {
     if (num_tiles <= 0) return 0;
     if (max_parts < 1 || max_parts > MERGE_MAX_PARTS || part_tiles < 1 || !queue || (max_parts > 1 && (!partial_o || !partial_ml)))
         return (int)cudaErrorInvalidValue;
@@ -853,6 +898,15 @@ static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, lon
     p.max_parts = max_parts;
     p.part_tiles = part_tiles;
     p.piece_rows = page_size % 64 == 0 ? 64 : page_size % 32 == 0 ? 32 : 16;
+    if (extras) {
+        p.chunk = extras->chunk;
+        p.keep_first = (window > 0 || extras->chunk > 0) ? extras->keep_first : 0;
+        p.maps = extras->maps;
+        p.softcap = extras->softcap;
+        p.out_scale = extras->out_scale;
+        p.sinks = extras->sinks;
+        p.out_f32 = extras->out_f32;
+    }
     // rows of head_dim elements that the cache maps cover: up to the last row of the last page
     const long long kv_rows = (long long)(num_pages - 1) * p.page_rows + (long long)(num_kv_heads - 1) * p.head_rows + page_size;
     if (kv_rows >= (1ll << 31)) return (int)cudaErrorInvalidValue;
@@ -911,4 +965,27 @@ EG_API int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q,
     return attention_prefill_tcgen05_any(stream, q, ldq, total_tokens, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo,
                                          num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, nullptr,
                                          max_parts, part_tiles, partial_o, partial_ml, queue, sink_logit * 1.4426950408889634f);
+}
+
+// The same with the further masks and score functions of Params: chunk, keep_first, softcap, sinks (float32 [num_heads],
+// natural-log logits, or null), maps (num_heads and num_kv_heads count rows and key heads; both planes hold num_kv_heads
+// heads), out_scale; out_dtype EG_BF16, or EG_F32 for float32 rows.
+EG_API int eg_attention_prefill_tcgen05_masked(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache,
+                                               const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out,
+                                               int out_dtype, long long ldo, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size,
+                                               long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale,
+                                               float softcap, const float* sinks, float out_scale, int* status, int max_parts, int part_tiles, float* partial_o,
+                                               float* partial_ml, int* queue) {
+    if (maps < 1 || num_kv_heads % maps || chunk < 0 || keep_first < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
+    Params extras{};
+    extras.chunk = chunk;
+    extras.keep_first = keep_first;
+    extras.maps = maps;
+    extras.softcap = softcap;
+    extras.out_scale = out_scale;
+    extras.sinks = sinks;
+    extras.out_f32 = out_dtype == EG_F32 ? (float*)out : nullptr;
+    return attention_prefill_tcgen05_any(stream, q, ldq, total_tokens, k_cache, v_cache, block_table, table_stride, positions, tiles, num_tiles, out, ldo,
+                                         num_heads, num_kv_heads, head_dim, page_size, page_stride, head_stride, num_pages, window, scale, status, nullptr,
+                                         max_parts, part_tiles, partial_o, partial_ml, queue, -INFINITY, &extras);
 }

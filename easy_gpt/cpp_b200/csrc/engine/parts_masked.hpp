@@ -21,7 +21,8 @@ namespace easygpt::engine {
 // out = W_o (heads' outputs side by side, times out_scale).  The cache keeps one row (keys | value) per token and key head;
 // where dim = vdim it keeps keys and values in planes of their own with a head per (key head, map), the value stored once per
 // map: G * maps ordinary key/value heads, which in bfloat16 (heads of 32, 64 or 128) the engine's tensor-core kernels walk: the
-// tiled one for prompt portions, the split-key one for single tokens; everything else runs on the generic kernel.  With a window
+// tcgen05 one for prompt portions of 33 tokens and more (heads of 64 and 128), the tiled mma.sync one for shorter portions and
+// heads of 32, the split-key one for single tokens; everything else runs on the generic kernel.  With a window
 // or a chunk the cache manager gives pages back that no coming token can see, except those of the kept first positions.
 // Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, maps, window, chunk, keep_first, softcap, sinks, qk_norm,
 // norm_eps, diff, out_scale.  Tensors: .q .k .v .o (+ .q.norm .k.norm, .sink, .lq1 .lk1 .lq2 .lk2).
@@ -83,7 +84,7 @@ public:
     size_t weight_bytes() const override { return qkv_.weight_bytes() + out_.weight_bytes(); }
     size_t arena_bytes(long long T) const override {
         // partial results of single tokens whose keys are dealt to several CTAs: bounded by the CTAs of a few waves
-        const size_t partials = planes() ? (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(dv_ + 2) * 4 : 0;
+        const size_t partials = planes() ? plans::PREFILL_PARTS_SCRATCH_BYTES + (size_t)(4 * plans::sm_count() + 64) * 128 * (size_t)(dv_ + 2) * 4 : 0;
         return (size_t)T * ((size_t)qkv_.out_features * 4 + (size_t)heads_ * maps_ * (dk_ + dv_) * 4 + (size_t)heads_ * dv_ * 4 + (size_t)hidden_ * 4) + partials + (1u << 16);
     }
     bool capturable() const override { return true; }
@@ -137,12 +138,30 @@ public:
                                                          cache.head_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_, scale_, softcap_, sinks,
                                                          factor, ctx.status), "attention_prefill_masked");
             };
-            // prompt portions in tiles of query tokens; single tokens (decoding, short entries) split over their keys
-            if (ctx.query_tiles) tiled(ctx.query_tiles, ctx.num_tiles);
+            // prompt portions in tiles of query tokens, on tcgen05 when they are long enough to fill its 128-row tiles; single
+            // tokens (decoding, short entries) split over their keys
+            const long long reach = kept_back() < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, kept_back() + keep_first_ + 255);
+            const int key_heads = kv_heads_ * maps_;
+            if (ctx.query_tiles && ctx.max_query_len >= plans::TCGEN05_ATTENTION_MIN_QUERY && plans::attention_prefill_tcgen05_takes(dtype, dk_, cache.page_size)) {
+                int parts, part_tiles;
+                plans::attention_prefill_parts(ctx.num_tiles, rows, dk_, reach, &parts, &part_tiles);
+                const size_t slots = (size_t)ctx.num_tiles * rows;
+                while (parts > 1 && slots * parts * 128 * (dk_ + 2) * 4 > plans::PREFILL_PARTS_SCRATCH_BYTES) --parts;
+                float *partial_o = nullptr, *partial_ml = nullptr;
+                if (parts > 1) {
+                    partial_o = ctx.take<float>(slots * parts * 128 * dk_);
+                    partial_ml = ctx.take<float>(slots * parts * 128 * 2);
+                }
+                launch_check(eg_attention_prefill_tcgen05_masked(ctx.stream, q.p, q.ld, T, cache.k, cache.v, tables.block_table, tables.table_width, ctx.positions,
+                                                                 ctx.query_tiles, ctx.num_tiles, out, (int)out_dtype, ldo, rows, key_heads, maps_, dk_, cache.page_size,
+                                                                 cache.page_stride, cache.head_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_,
+                                                                 scale_, softcap_, sinks, factor, ctx.status, parts, part_tiles, partial_o, partial_ml,
+                                                                 ctx.scratch->prefill_queue.as<int>()), "attention_prefill_tcgen05_masked");
+            } else if (ctx.query_tiles) {
+                tiled(ctx.query_tiles, ctx.num_tiles);
+            }
             const int singles = ctx.query_tiles ? ctx.num_small : T;
             if (singles > 0) {
-                const long long reach = kept_back() < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, kept_back() + keep_first_ + 255);
-                const int key_heads = kv_heads_ * maps_;
                 const int splits = plans::attention_paged_splits(singles, rows, key_heads, reach, dk_);
                 float *acc = nullptr, *ml = nullptr;
                 int* counters = nullptr;
