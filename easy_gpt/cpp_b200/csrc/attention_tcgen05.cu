@@ -230,11 +230,13 @@ struct Params {
     int piece_rows;            // keys a TMA box of K or V holds: 64, 32 or 16, a divisor of the page size
     // Further masks and score functions (all off by default).  chunk: a query sees keys of its own block of `chunk` positions
     // only; keep_first: keys 0 .. keep_first - 1 stay visible whatever window and chunk say (their key tiles are walked first);
-    // softcap c: the scaled score becomes c tanh(score / c); sinks: a logit per query row (natural log) in place of sink2;
+    // sinks: a logit per query row (natural log) in place of sink2;
     // maps m: query rows head * m + map read key head (head / group) * m + map (both planes hold num_kv_heads heads; num_heads
     // counts rows); out_scale: a factor on the output; out_f32: float32 output [tokens, ldo] instead of `out`.
+    // (A soft cap on the scores was built in here and measured: a second exponent a score in softmax threads that run at the
+    // exponent unit's rate already; the tiled mma.sync kernel was faster with it and keeps it.)
     int chunk = 0, keep_first = 0, maps = 1;
-    float softcap = 0.f, out_scale = 1.f;
+    float out_scale = 1.f;
     const float* sinks = nullptr;
     float* out_f32 = nullptr;
 };
@@ -248,11 +250,7 @@ __device__ __forceinline__ int first_visible(const Params& p, int pos) {
 // others (this many), then the tiles from all_lo, the tile of the first visible key, on.
 __device__ __forceinline__ int kept_tiles_of(const Params& p, int all_lo) { return p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, all_lo) : 0; }
 __device__ __forceinline__ float sink_of(const Params& p, int h) { return p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2; }
-// tanh by one exponent and one division: absolute error about 1e-7, which a score that goes into an exponent next can bear
-__device__ __forceinline__ float tanh_by_exp(float x) {
-    const float e = __expf(2.0f * fminf(x, 15.0f));
-    return 1.0f - __fdividef(2.0f, e + 1.0f);
-}
+
 
 // acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
 // sink's term 2^(sink2 - m) joining the sum (in a form that cannot overflow whatever m is)
@@ -496,9 +494,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
             const int warp_first = first_visible(p, warp_lo), row_first = first_visible(p, qpos);
             const bool warp_has_rows = quad * 32 < count;
-            // with a soft cap the scores are scaled and capped as they come out of TMEM; else the scale rides in the exponent
-            const float scale_log2 = p.softcap > 0.f ? 1.4426950408889634f : p.scale * 1.4426950408889634f;
-            const float cap_pre = p.softcap > 0.f ? p.scale / p.softcap : 0.f;
+            const float scale_log2 = p.scale * 1.4426950408889634f;
             const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
             const uint32_t o_lane = lane_base + (uint32_t)(S::O_COL + g * HD);
 
@@ -533,10 +529,6 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     }
                     STAMP(2)
                     // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
-                    if (p.softcap > 0.f) {
-#pragma unroll
-                        for (int e = 0; e < 64; ++e) s[e] = p.softcap * tanh_by_exp(s[e] * cap_pre);
-                    }
                     // (also a tile with kept first keys, and one in which a chunk of some row of the warp begins)
                     const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count || key_base < first_visible(p, warp_lo + 31) ||
                                         key_base < p.keep_first;
@@ -902,7 +894,6 @@ static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, lon
         p.chunk = extras->chunk;
         p.keep_first = (window > 0 || extras->chunk > 0) ? extras->keep_first : 0;
         p.maps = extras->maps;
-        p.softcap = extras->softcap;
         p.out_scale = extras->out_scale;
         p.sinks = extras->sinks;
         p.out_f32 = extras->out_f32;
@@ -967,21 +958,20 @@ EG_API int eg_attention_prefill_tcgen05_sink(cudaStream_t stream, const void* q,
                                          max_parts, part_tiles, partial_o, partial_ml, queue, sink_logit * 1.4426950408889634f);
 }
 
-// The same with the further masks and score functions of Params: chunk, keep_first, softcap, sinks (float32 [num_heads],
-// natural-log logits, or null), maps (num_heads and num_kv_heads count rows and key heads; both planes hold num_kv_heads
+// The same with the further masks of Params: chunk, keep_first, sinks (float32 [num_heads], natural-log logits, or null),
+// maps (num_heads and num_kv_heads count rows and key heads; both planes hold num_kv_heads
 // heads), out_scale; out_dtype EG_BF16, or EG_F32 for float32 rows.
 EG_API int eg_attention_prefill_tcgen05_masked(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache,
                                                const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out,
                                                int out_dtype, long long ldo, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size,
                                                long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale,
-                                               float softcap, const float* sinks, float out_scale, int* status, int max_parts, int part_tiles, float* partial_o,
+                                               const float* sinks, float out_scale, int* status, int max_parts, int part_tiles, float* partial_o,
                                                float* partial_ml, int* queue) {
-    if (maps < 1 || num_kv_heads % maps || chunk < 0 || keep_first < 0 || softcap < 0.f) return (int)cudaErrorInvalidValue;
+    if (maps < 1 || num_kv_heads % maps || chunk < 0 || keep_first < 0) return (int)cudaErrorInvalidValue;
     Params extras{};
     extras.chunk = chunk;
     extras.keep_first = keep_first;
     extras.maps = maps;
-    extras.softcap = softcap;
     extras.out_scale = out_scale;
     extras.sinks = sinks;
     extras.out_f32 = out_dtype == EG_F32 ? (float*)out : nullptr;

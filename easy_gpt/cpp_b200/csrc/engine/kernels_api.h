@@ -182,5 +182,5 @@ int eg_gemm_tcgen05_pair_glu_bias(cudaStream_t stream, const void* A, long long 
 // sandwich.cu
 int eg_rmsnorm_add_rows(cudaStream_t stream, float* residual, const void* y, int y_dtype, long long ldy, const float* bias, const float* gain, float eps, void* out, int out_dtype, int tokens, int hidden);
 // attention_tcgen05.cu
-int eg_attention_prefill_tcgen05_masked(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int out_dtype, long long ldo, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale, float softcap, const float* sinks, float out_scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue);
+int eg_attention_prefill_tcgen05_masked(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache, const void* v_cache, const int* block_table, int table_stride, const int* positions, const int* tiles, int num_tiles, void* out, int out_dtype, long long ldo, int num_heads, int num_kv_heads, int maps, int head_dim, int page_size, long long page_stride, long long head_stride, int num_pages, int window, int chunk, int keep_first, float scale, const float* sinks, float out_scale, int* status, int max_parts, int part_tiles, float* partial_o, float* partial_ml, int* queue);
 }  // extern "C"

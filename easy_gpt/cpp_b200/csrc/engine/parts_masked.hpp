@@ -21,8 +21,8 @@ namespace easygpt::engine {
 // out = W_o (heads' outputs side by side, times out_scale).  The cache keeps one row (keys | value) per token and key head;
 // where dim = vdim it keeps keys and values in planes of their own with a head per (key head, map), the value stored once per
 // map: G * maps ordinary key/value heads, which in bfloat16 (heads of 32, 64 or 128) the engine's tensor-core kernels walk: the
-// tcgen05 one for prompt portions of 33 tokens and more (heads of 64 and 128), the tiled mma.sync one for shorter portions and
-// heads of 32, the split-key one for single tokens; everything else runs on the generic kernel.  With a window
+// tcgen05 one for prompt portions of 33 tokens and more (heads of 64 and 128, no soft cap), the tiled mma.sync one for shorter
+// portions, heads of 32 and capped scores, the split-key one for single tokens; everything else runs on the generic kernel.  With a window
 // or a chunk the cache manager gives pages back that no coming token can see, except those of the kept first positions.
 // Parameters: hidden_size, heads, kv_heads, dim, vdim, scale, maps, window, chunk, keep_first, softcap, sinks, qk_norm,
 // norm_eps, diff, out_scale.  Tensors: .q .k .v .o (+ .q.norm .k.norm, .sink, .lq1 .lk1 .lq2 .lk2).
@@ -142,7 +142,11 @@ public:
             // tokens (decoding, short entries) split over their keys
             const long long reach = kept_back() < 0 ? ctx.max_context_len : std::min<long long>(ctx.max_context_len, kept_back() + keep_first_ + 255);
             const int key_heads = kv_heads_ * maps_;
-            if (ctx.query_tiles && ctx.max_query_len >= plans::TCGEN05_ATTENTION_MIN_QUERY && plans::attention_prefill_tcgen05_takes(dtype, dk_, cache.page_size)) {
+            // (with a soft cap the tiled kernel: the cap is a second exponent a score, and the tcgen05 kernel's softmax threads run at
+            // the exponent unit's rate already; measured on B200, 8 heads of 128, 2,048 tokens, window 1,024, 64 kept keys: 56 us
+            // tiled, 57 us + 11 us for the merge of its parts on tcgen05)
+            if (ctx.query_tiles && softcap_ == 0.f && ctx.max_query_len >= plans::TCGEN05_ATTENTION_MIN_QUERY &&
+                plans::attention_prefill_tcgen05_takes(dtype, dk_, cache.page_size)) {
                 int parts, part_tiles;
                 plans::attention_prefill_parts(ctx.num_tiles, rows, dk_, reach, &parts, &part_tiles);
                 const size_t slots = (size_t)ctx.num_tiles * rows;
@@ -155,7 +159,7 @@ public:
                 launch_check(eg_attention_prefill_tcgen05_masked(ctx.stream, q.p, q.ld, T, cache.k, cache.v, tables.block_table, tables.table_width, ctx.positions,
                                                                  ctx.query_tiles, ctx.num_tiles, out, (int)out_dtype, ldo, rows, key_heads, maps_, dk_, cache.page_size,
                                                                  cache.page_stride, cache.head_stride, cache.num_pages, (int)window_, (int)chunk_, (int)keep_first_,
-                                                                 scale_, softcap_, sinks, factor, ctx.status, parts, part_tiles, partial_o, partial_ml,
+                                                                 scale_, sinks, factor, ctx.status, parts, part_tiles, partial_o, partial_ml,
                                                                  ctx.scratch->prefill_queue.as<int>()), "attention_prefill_tcgen05_masked");
             } else if (ctx.query_tiles) {
                 tiled(ctx.query_tiles, ctx.num_tiles);

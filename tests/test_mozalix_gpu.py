@@ -311,10 +311,10 @@ EDGES = {
     "chunk": (lambda dim: chunked(heads=2, kv_heads=1, dim=dim, vdim=dim, size=20, rot_dims=4),
               {"inside": lambda end: end // 20 * 20, "outside": lambda end: end // 20 * 20 - 1},
               lambda m, which: None),
-    "kept_window": (lambda dim: side(left=(2, 1, dim, dim, 0.3), right=(2, 1, 8, 8, 3), size=20, keep_first=5, softcap=30.0),
+    "kept_window": (lambda dim: side(left=(2, 1, dim, dim, 0.3), right=(2, 1, 8, 8, 3), size=20, keep_first=5, softcap=30.0 if dim == 16 else None),
                     {"inside": lambda end: end - 19, "outside": lambda end: end - 20},
                     lambda m, which: m["left"]["mask"].update(size=19 if which == "inside" else 21)),
-    "kept_first": (lambda dim: side(left=(2, 1, dim, dim, 0.3), right=(2, 1, 8, 8, 3), size=20, keep_first=5, softcap=30.0),
+    "kept_first": (lambda dim: side(left=(2, 1, dim, dim, 0.3), right=(2, 1, 8, 8, 3), size=20, keep_first=5, softcap=30.0 if dim == 16 else None),
                    {"inside": lambda end: 4, "outside": lambda end: 5},
                    lambda m, which: m["left"]["mask"].update(keep_first=4 if which == "inside" else 6)),
 }
@@ -407,14 +407,16 @@ def test_far_keys_sinks_and_slow_states(folders, dtype, dim):
         assert np.abs(pm.forward(c2, w2, short) - want[:64]).max() > 4 * TOL[dtype] * np.abs(want).max(), name
 
 
-def test_long_masks_over_several_ctas(folders):
+@pytest.mark.parametrize("cap", [14.0, None])
+def test_long_masks_over_several_ctas(folders, cap):
     """Masks of hundreds of positions on the tensor-core path: a single token's keys are then dealt to several CTAs, the tiles of
     the kept first keys among them, and a prompt tile walks kept tiles, then its window's.  One kept key far back is the one
-    that the last tokens look for (sharp weights), in a portion's tail and while two requests decode side by side."""
-    cfg, over = aimed(model([(side(left=(4, 2, 64, 64, 0.3), right=(2, 1, 16, 16, 3), size=700, keep_first=70, softcap=14.0), None),
+    that the last tokens look for (sharp weights), in a portion's tail and while two requests decode side by side.  With a cap the
+    first layer's prompt portions run on the tiled kernel, without on tcgen05, where the tile's keys are cut into parts."""
+    cfg, over = aimed(model([(side(left=(4, 2, 64, 64, 0.3), right=(2, 1, 16, 16, 3), size=700, keep_first=70, softcap=cap), None),
                              (chunked(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, size=640, rot_dims=16), None),
                              (two_maps(heads=2, kv_heads=1, dim=32, vdim=32, scale=0.2, size=800, rot_dims=8), None)], vocab=140, width=128), 9, 138, 139)
-    folder, cfg, w = folders("long_masks", cfg, seed=9, overrides=over)
+    folder, cfg, w = folders(f"long_masks{cap}", cfg, seed=9, overrides=over)
     n = 1440
     toks = tokens(130, n, 77)
     toks[69] = 139                                                # the last kept position
