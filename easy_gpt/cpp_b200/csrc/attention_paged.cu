@@ -104,8 +104,14 @@ __device__ __forceinline__ float norm_with_sink(float m, float l, float sink2) {
     return c / fmaf(l, c, exp2f(sink2 - top));
 }
 
-template <int HD, bool DEEP, int TPI, int KW>
+// MASKED: the further masks and score functions of Params are read; without it they are constants ("none"), and the kernel is the
+// plain one to the instruction.
+template <int HD, bool DEEP, int TPI, int KW, bool MASKED>
 __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Params p) {
+    const int x_chunk = MASKED ? p.chunk : 0, x_keep = MASKED ? p.keep_first : 0, x_maps = MASKED ? p.maps : 1;
+    const float x_softcap = MASKED ? p.softcap : 0.f, x_out_scale = MASKED ? p.out_scale : 1.f;
+    const float* const x_sinks = MASKED ? p.sinks : nullptr;
+    float* const x_out_f32 = MASKED ? p.out_f32 : nullptr;
     constexpr int TI = TPI * KW / 16;                                // key tiles of an iteration
     constexpr int KB = KW / 16;                                      // blocks of 16 keys a warp takes of its tile
     using L = Layout<HD, DEEP, TPI, TI>;
@@ -121,10 +127,10 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     const int g0 = (blockIdx.y % gblocks) * 16;                   // first query head of the group handled here
     const int split = blockIdx.z;
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const float cap_pre = p.softcap > 0.f ? p.scale / p.softcap : 0.f, cap_post = p.softcap * 1.4426950408889634f;
+    const float cap_pre = x_softcap > 0.f ? p.scale / x_softcap : 0.f, cap_post = x_softcap * 1.4426950408889634f;
     // the query row (and output row) of row r of this key head's group, and its sink (base 2)
-    auto head_of = [&](int r) { return p.maps == 1 ? kvh * G + r : ((kvh / p.maps) * G + r) * p.maps + kvh % p.maps; };
-    auto sink_of = [&](int r) { return p.sinks ? p.sinks[head_of(r)] * 1.4426950408889634f : p.sink2; };
+    auto head_of = [&](int r) { return x_maps == 1 ? kvh * G + r : ((kvh / x_maps) * G + r) * x_maps + kvh % x_maps; };
+    auto sink_of = [&](int r) { return x_sinks ? x_sinks[head_of(r)] * 1.4426950408889634f : p.sink2; };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
 
@@ -146,15 +152,15 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
     const int pos = p.positions[t];
     const int fresh_from = p.seq_context ? p.seq_context[p.token_seq[t]] : 0;
     int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    if (p.chunk > 0) first = max(first, pos / p.chunk * p.chunk);
+    if (x_chunk > 0) first = max(first, pos / x_chunk * x_chunk);
     const int* table = p.block_table + (size_t)p.token_seq[t] * p.table_stride;
     const int tile_lo = first / TILE_KEYS, tile_hi = pos / TILE_KEYS;           // inclusive
     // Key tiles in the order they are walked: those of the kept first keys that lie wholly in front of the others, then the
     // tiles from the first visible key on.  my_lo, my_hi and every tile index below count in that order; tile_of gives the tile.
-    const int kept_tiles = p.keep_first > 0 ? min((p.keep_first + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
+    const int kept_tiles = x_keep > 0 ? min((x_keep + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
     const int all_tiles = kept_tiles + tile_hi - tile_lo + 1;
     auto tile_of = [&](int w) { return w < kept_tiles ? w : tile_lo + w - kept_tiles; };
-    auto visible = [&](int kpos) { return (kpos >= first || kpos < p.keep_first) && kpos <= pos; };
+    auto visible = [&](int kpos) { return (kpos >= first || kpos < x_keep) && kpos <= pos; };
     const int per = (all_tiles + p.splits - 1) / p.splits;
     const int my_lo = split * per;
     const int my_hi = min(all_tiles - 1, my_lo + per - 1);
@@ -170,7 +176,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         for (int e = threadIdx.x; e < count * 4; e += NT) {
             const int kpos0 = tile_of(tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
             long long base = -1;
-            if (kpos0 <= pos && (kpos0 + 15 >= first || kpos0 < p.keep_first)) {
+            if (kpos0 <= pos && (kpos0 + 15 >= first || kpos0 < x_keep)) {
                 const int page = table[kpos0 / p.page_size];
                 if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
                 else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
@@ -265,7 +271,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         const unsigned char* vs = ks + L::TILE_BYTES;
         if (it * TI + group >= ntiles) continue;                                  // the run has no tile for this group of warps any more
         const int key_base = tile_of(my_lo + it * TI + group) * TILE_KEYS + key0; // this warp's KW keys
-        if (key_base > pos || (key_base + KW - 1 < first && key_base >= p.keep_first)) continue;   // nothing visible in them
+        if (key_base > pos || (key_base + KW - 1 < first && key_base >= x_keep)) continue;   // nothing visible in them
 
         // S = Q K^T for 16 rows x KW keys
         float s[2 * KB][4];
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
             for (int e = 0; e < 4; ++e) {
                 const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
                 const bool ok = visible(kpos);
-                s[j][e] = ok ? (p.softcap > 0.f ? cap_post * tanh_by_exp(s[j][e] * cap_pre) : s[j][e] * scale_log2) : -INFINITY;
+                s[j][e] = ok ? (x_softcap > 0.f ? cap_post * tanh_by_exp(s[j][e] * cap_pre) : s[j][e] * scale_log2) : -INFINITY;
                 if (e < 2) tmax0 = fmaxf(tmax0, s[j][e]); else tmax1 = fmaxf(tmax1, s[j][e]);
             }
         tmax0 = fmaxf(tmax0, __shfl_xor_sync(0xffffffffu, tmax0, 1));
@@ -395,9 +401,9 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         const int h = kvh * G + g0 + r;
         if (p.splits == 1) {
             const float s2 = sink_of(g0 + r);
-            const float v = (s2 == -INFINITY ? (l > 0.f ? a / l : 0.f) : a * norm_with_sink(m, l, s2)) * p.out_scale;
+            const float v = (s2 == -INFINITY ? (l > 0.f ? a / l : 0.f) : a * norm_with_sink(m, l, s2)) * x_out_scale;
             const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + d;
-            if (p.out_f32) p.out_f32[at] = v;
+            if (x_out_f32) x_out_f32[at] = v;
             else p.out[at] = __float2bfloat16_rn(v);
         } else if (p.cluster_merge) {
             const uint32_t at = incoming + (uint32_t)((cluster_rank * rows + r) * (HD + 2)) * 4u;
@@ -438,9 +444,9 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                 const float2 lo = *reinterpret_cast<const float2*>(part + dq * 4), hi = *reinterpret_cast<const float2*>(part + dq * 4 + 2);
                 a.x += lo.x * w; a.y += lo.y * w; a.z += hi.x * w; a.w += hi.y * w;
             }
-            const float il = norm_with_sink(m, l, sink_of(g0 + r)) * p.out_scale;
+            const float il = norm_with_sink(m, l, sink_of(g0 + r)) * x_out_scale;
             const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + dq * 4;
-            if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
+            if (x_out_f32) *reinterpret_cast<float4*>(x_out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
             else *reinterpret_cast<uint2*>(p.out + at) = make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
         }
         return;
@@ -495,7 +501,7 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
                     f[s2] = w;
                     l += lp[s2] * w;
                 }
-                inv_l[threadIdx.x] = norm_with_sink(m, l, sink_of(g0 + threadIdx.x)) * p.out_scale;
+                inv_l[threadIdx.x] = norm_with_sink(m, l, sink_of(g0 + threadIdx.x)) * x_out_scale;
             }
             __syncthreads();
         }
@@ -521,17 +527,17 @@ __global__ void __launch_bounds__(TPI * THREADS) attention_paged_kernel(const Pa
         }
         const float il = inv_l[r];
         const size_t at = (size_t)t * p.ldo + (size_t)head_of(g0 + r) * HD + dq * 4;
-        if (p.out_f32) *reinterpret_cast<float4*>(p.out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
+        if (x_out_f32) *reinterpret_cast<float4*>(x_out_f32 + at) = make_float4(a.x * il, a.y * il, a.z * il, a.w * il);
         else *reinterpret_cast<uint2*>(p.out + at) = make_uint2(pack_bf16(a.x * il, a.y * il), pack_bf16(a.z * il, a.w * il));
     }
 }
 
-template <int HD, bool DEEP, int TPI = 1, int KW = 16>
+template <int HD, bool DEEP, bool MASKED, int TPI = 1, int KW = 16>
 int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_cluster = false) {
     using L = Layout<HD, DEEP, TPI, TPI * KW / 16>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -566,7 +572,7 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
     if (cluster_allowed && ((DEEP && ctas <= sms) || (!DEEP && p.splits <= 8)) && p.splits > 1 && p.splits <= 16 &&
         L::WARP_MERGE_BYTES + incoming_bytes <= (size_t)L::SMEM) {
         static int leave = 0;                                                      // 0 not asked yet, 1 given, -1 refused
-        if (!leave) leave = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : -1;
+        if (!leave) leave = cudaFuncSetAttribute(attention_paged_kernel<HD, DEEP, TPI, KW, MASKED>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess ? 1 : -1;
         if (p.splits <= 8 || leave == 1) {
             attr[nattr].id = cudaLaunchAttributeClusterDimension;
             attr[nattr].val.clusterDim.x = 1;
@@ -577,7 +583,7 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
             int clusters = 0;
             // all clusters have to be on the GPU together, or the last ones run as a second wave (measured: batch 8, 16
             // clusters of 8 CTAs, of which 15 found room: the step took 0.92 ms instead of 0.80)
-            if (cudaOccupancyMaxActiveClusters(&clusters, attention_paged_kernel<HD, DEEP, TPI, KW>, &cfg) == cudaSuccess &&
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_paged_kernel<HD, DEEP, TPI, KW, MASKED>, &cfg) == cudaSuccess &&
                 clusters >= (int)(grid.x * grid.y)) {
                 q.cluster_merge = 1;
                 ++nattr;
@@ -589,10 +595,10 @@ int launch_with(cudaStream_t stream, const Params& p, dim3 grid, bool must_clust
     if (must_cluster && !q.cluster_merge) return -1;                              // the caller has another way
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
-    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP, TPI, KW>, q);
+    return (int)cudaLaunchKernelEx(&cfg, attention_paged_kernel<HD, DEEP, TPI, KW, MASKED>, q);
 }
 
-template <int HD>
+template <int HD, bool MASKED>
 int launch(cudaStream_t stream, const Params& p, int tokens) {
     static int sm_count = 0;
     if (!sm_count) {
@@ -620,11 +626,11 @@ int launch(cudaStream_t stream, const Params& p, int tokens) {
             // long runs: only if the clusters still cover most of the SMs (7B sizes, batch 8, context 8k: 4.05 ms a step with
             // 32 clusters of 4, 5.08 with 256 four-warp CTAs and tickets)
             if (most_tiles > 16ll * half.splits && (long long)grid.x * grid.y * half.splits * 100 < 85ll * sm_count) break;
-            const int rc = launch_with<HD, true, 2, WIDE_KEYS>(stream, half, dim3(grid.x, grid.y, half.splits), true);
+            const int rc = launch_with<HD, true, MASKED, 2, WIDE_KEYS>(stream, half, dim3(grid.x, grid.y, half.splits), true);
             if (rc != -1) return rc;
         }
     }
-    return ctas <= 2ll * sm_count ? launch_with<HD, true>(stream, p, grid) : launch_with<HD, false>(stream, p, grid);
+    return ctas <= 2ll * sm_count ? launch_with<HD, true, MASKED>(stream, p, grid) : launch_with<HD, false, MASKED>(stream, p, grid);
 }
 
 
@@ -680,8 +686,12 @@ struct PrefillLayout {
     static constexpr int SMEM = STAGES * STAGE_BYTES;
 };
 
-template <int HD>
+template <int HD, bool MASKED>
 __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_kernel(const PrefillParams p) {
+    const int x_chunk = MASKED ? p.chunk : 0, x_keep = MASKED ? p.keep_first : 0, x_maps = MASKED ? p.maps : 1;
+    const float x_softcap = MASKED ? p.softcap : 0.f, x_out_scale = MASKED ? p.out_scale : 1.f;
+    const float* const x_sinks = MASKED ? p.sinks : nullptr;
+    float* const x_out_f32 = MASKED ? p.out_f32 : nullptr;
     using L = Layout<HD>;
     using PL = PrefillLayout<HD>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -689,10 +699,10 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     const int item = gridDim.x - 1 - blockIdx.x;
     const int tile = item >> 1, half = item & 1;                 // a listed tile has up to 128 tokens: two CTAs
     const int h = blockIdx.y;
-    const int kvh = (h / p.maps) / (p.num_heads / p.num_kv_heads) * p.maps + h % p.maps;
+    const int kvh = (h / x_maps) / (p.num_heads / p.num_kv_heads) * x_maps + h % x_maps;
     // with a soft cap the scores are scaled and capped as they come out of the product; else the scale rides in the exponent
-    const float scale_log2 = p.softcap > 0.f ? 1.4426950408889634f : p.scale * 1.4426950408889634f;
-    const float sink2 = p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2;
+    const float scale_log2 = x_softcap > 0.f ? 1.4426950408889634f : p.scale * 1.4426950408889634f;
+    const float sink2 = x_sinks ? x_sinks[h] * 1.4426950408889634f : p.sink2;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1] + half * TILE_KEYS;
@@ -703,13 +713,13 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     // the first key that the window and the chunk of a query at `pos` leave visible (never decreasing in pos)
     auto first_of = [&](int pos) {
         const int w = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-        return p.chunk > 0 ? max(w, pos / p.chunk * p.chunk) : w;
+        return x_chunk > 0 ? max(w, pos / x_chunk * x_chunk) : w;
     };
     const int first = first_of(pos_lo);
     const int tile_lo = first / TILE_KEYS;
     // key tiles in the order they are walked: those of the kept first keys that lie wholly in front of the others, then the
     // tiles from the first visible key on
-    const int kept_tiles = p.keep_first > 0 ? min((p.keep_first + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
+    const int kept_tiles = x_keep > 0 ? min((x_keep + TILE_KEYS - 1) / TILE_KEYS, tile_lo) : 0;
     const int ntiles = kept_tiles + pos_hi / TILE_KEYS - tile_lo + 1;
     auto tile_of = [&](int it) { return it < kept_tiles ? it : tile_lo + it - kept_tiles; };
 
@@ -739,7 +749,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
         for (int e = threadIdx.x; e < count * 4; e += THREADS) {
             const int kpos0 = tile_of(tile0 + e / 4) * TILE_KEYS + (e % 4) * 16;
             long long base = -1;
-            if (kpos0 <= pos_hi && (kpos0 + 15 >= first || kpos0 < p.keep_first)) {
+            if (kpos0 <= pos_hi && (kpos0 + 15 >= first || kpos0 < x_keep)) {
                 const int page = table[kpos0 / p.page_size];
                 if (page < 0 || page >= p.num_pages) atomicOr(p.status, EG_STATUS_BAD_PAGE);
                 else base = (long long)page * p.page_stride + (long long)kvh * p.head_stride + (long long)(kpos0 % p.page_size) * HD;
@@ -759,7 +769,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
             const int row = e / L::CHUNKS, chunk = e % L::CHUNKS;
             const int kpos = kt * TILE_KEYS + row;
             const long long base = qb[row >> 4];
-            const bool valid = (kpos >= first || kpos < p.keep_first) && kpos <= pos_hi && base >= 0;
+            const bool valid = (kpos >= first || kpos < x_keep) && kpos <= pos_hi && base >= 0;
             const long long off = valid ? base + (long long)(row & 15) * HD + chunk * 8 : 0;
             cp_async_16(ks + L::offset(row, chunk), p.k_cache + off, valid);
             cp_async_16(vs + L::offset(row, chunk), p.v_cache + off, valid);
@@ -794,7 +804,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
         // this warp's rows see keys up to qp1 (or qp0): skip a key tile that lies wholly behind or before them (kept first keys are never before them)
         const int warp_hi = pos_lo + min(count - 1, warp * 16 + 15), warp_lo = pos_lo + warp * 16;
         const int warp_first = first_of(warp_lo);
-        if (warp * 16 >= count || key_base > warp_hi || (key_base + TILE_KEYS - 1 < warp_first && key_base >= p.keep_first)) continue;
+        if (warp * 16 >= count || key_base > warp_hi || (key_base + TILE_KEYS - 1 < warp_first && key_base >= x_keep)) continue;
 
         float s[8][4];
 #pragma unroll
@@ -812,12 +822,12 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
         }
         // Scores stay unscaled here; the scale goes into the exponent's multiply-add.  Only a tile that crosses the
         // diagonal, the window's far edge or the end of the portion needs the per-element limits.
-        if (p.softcap > 0.f) {
-            const float pre = p.scale / p.softcap;
+        if (x_softcap > 0.f) {
+            const float pre = p.scale / x_softcap;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[j][e] = p.softcap * tanh_by_exp(s[j][e] * pre);
+                for (int e = 0; e < 4; ++e) s[j][e] = x_softcap * tanh_by_exp(s[j][e] * pre);
         }
         const bool limits = key_base + TILE_KEYS - 1 > warp_lo || warp * 16 + 15 >= count || key_base < first_of(warp_lo + 15);
         if (limits) {
@@ -828,7 +838,7 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
                 for (int e = 0; e < 4; ++e) {
                     const int kpos = key_base + j * 8 + 2 * tig + (e & 1);
                     const int qp = e < 2 ? qp0 : qp1;
-                    const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (kpos >= (e < 2 ? f0 : f1) || kpos < p.keep_first);
+                    const bool ok = (e < 2 ? v0 : v1) && kpos <= qp && (kpos >= (e < 2 ? f0 : f1) || kpos < x_keep);
                     if (!ok) s[j][e] = -INFINITY;
                 }
         }
@@ -891,13 +901,13 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float i0 = norm_with_sink(m0, l0, sink2) * p.out_scale, i1 = norm_with_sink(m1, l1, sink2) * p.out_scale;
+    const float i0 = norm_with_sink(m0, l0, sink2) * x_out_scale, i1 = norm_with_sink(m1, l1, sink2) * x_out_scale;
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
         const int d = i * 8 + 2 * tig;
-        if (p.out_f32) {
-            if (v0) *reinterpret_cast<float2*>(p.out_f32 + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][0] * i0, acc[i][1] * i0);
-            if (v1) *reinterpret_cast<float2*>(p.out_f32 + (size_t)(t0 + r1) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][2] * i1, acc[i][3] * i1);
+        if (x_out_f32) {
+            if (v0) *reinterpret_cast<float2*>(x_out_f32 + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][0] * i0, acc[i][1] * i0);
+            if (v1) *reinterpret_cast<float2*>(x_out_f32 + (size_t)(t0 + r1) * p.ldo + (size_t)h * HD + d) = make_float2(acc[i][2] * i1, acc[i][3] * i1);
             continue;
         }
         if (v0) *reinterpret_cast<uint32_t*>(p.out + (size_t)(t0 + r0) * p.ldo + (size_t)h * HD + d) = pack_bf16(acc[i][0] * i0, acc[i][1] * i0);
@@ -905,17 +915,17 @@ __global__ void __launch_bounds__(THREADS, HD <= 64 ? 4 : 2) attention_prefill_k
     }
 }
 
-template <int HD>
+template <int HD, bool MASKED = false>
 int launch_prefill(cudaStream_t stream, const PrefillParams& p, int num_tiles) {
     using PL = PrefillLayout<HD>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, PL::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, PL::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(2 * num_tiles, p.num_heads);
-    attention_prefill_kernel<HD><<<grid, THREADS, PL::SMEM, stream>>>(p);
+    attention_prefill_kernel<HD, MASKED><<<grid, THREADS, PL::SMEM, stream>>>(p);
     return eg_launch_status();
 }
 
@@ -953,11 +963,19 @@ static int attention_paged_any(cudaStream_t stream, const void* q, int ldq, cons
         p.sinks = extras->sinks;
         p.out_f32 = extras->out_f32;
     }
+    if (extras) {
+        switch (head_dim) {
+            case 32: return launch<32, true>(stream, p, tokens);
+            case 64: return launch<64, true>(stream, p, tokens);
+            case 128: return launch<128, true>(stream, p, tokens);
+            default: return (int)cudaErrorInvalidValue;
+        }
+    }
     switch (head_dim) {
-        case 32: return launch<32>(stream, p, tokens);
-        case 64: return launch<64>(stream, p, tokens);
-        case 128: return launch<128>(stream, p, tokens);
-        case 256: return launch<256>(stream, p, tokens);
+        case 32: return launch<32, false>(stream, p, tokens);
+        case 64: return launch<64, false>(stream, p, tokens);
+        case 128: return launch<128, false>(stream, p, tokens);
+        case 256: return launch<256, false>(stream, p, tokens);
         default: return (int)cudaErrorInvalidValue;
     }
 }
@@ -1049,9 +1067,9 @@ EG_API int eg_attention_prefill_masked(cudaStream_t stream, const void* q, int l
     p.out_scale = out_scale;
     if (out_dtype == EG_F32) p.out_f32 = (float*)out;
     switch (head_dim) {
-        case 32: return launch_prefill<32>(stream, p, num_tiles);
-        case 64: return launch_prefill<64>(stream, p, num_tiles);
-        case 128: return launch_prefill<128>(stream, p, num_tiles);
+        case 32: return launch_prefill<32, true>(stream, p, num_tiles);
+        case 64: return launch_prefill<64, true>(stream, p, num_tiles);
+        case 128: return launch_prefill<128, true>(stream, p, num_tiles);
         default: return (int)cudaErrorInvalidValue;
     }
 }

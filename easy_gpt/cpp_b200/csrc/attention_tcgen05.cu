@@ -241,15 +241,21 @@ struct Params {
     float* out_f32 = nullptr;
 };
 
+// MASKED (a template parameter of the kernels): the further masks are read; without it they are constants ("none"), and the
+// kernels are the plain ones to the instruction.
 // the first key that the window and the chunk of a query at `pos` leave visible (never decreasing in pos)
-__device__ __forceinline__ int first_visible(const Params& p, int pos) {
+template <bool MASKED> __device__ __forceinline__ int first_visible(const Params& p, int pos) {
     const int w = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    return p.chunk > 0 ? max(w, pos / p.chunk * p.chunk) : w;
+    return MASKED && p.chunk > 0 ? max(w, pos / p.chunk * p.chunk) : w;
 }
 // A query tile's key tiles in the order they are walked: the tiles of the kept first keys that lie wholly in front of the
 // others (this many), then the tiles from all_lo, the tile of the first visible key, on.
-__device__ __forceinline__ int kept_tiles_of(const Params& p, int all_lo) { return p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, all_lo) : 0; }
-__device__ __forceinline__ float sink_of(const Params& p, int h) { return p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2; }
+template <bool MASKED> __device__ __forceinline__ int kept_tiles_of(const Params& p, int all_lo) {
+    return MASKED && p.keep_first > 0 ? min((p.keep_first + BN - 1) / BN, all_lo) : 0;
+}
+template <bool MASKED> __device__ __forceinline__ float sink_of(const Params& p, int h) {
+    return MASKED && p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink2;
+}
 
 
 // acc * this = the softmax's output, with (m, l) the reference (base 2) and sum of the weights that acc holds, and the
@@ -267,11 +273,14 @@ __device__ __forceinline__ uint64_t desc_from(uint32_t lo, uint32_t hi) {
     asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
-template <int HD, int WGS>
+template <int HD, int WGS, bool MASKED>
 __global__ void __launch_bounds__((Shape<HD, WGS>::THREADS), (Shape<HD, WGS>::CTAS_PER_SM))
 attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const Params p) {
     using S = Shape<HD, WGS>;
+    const int x_keep = MASKED ? p.keep_first : 0, x_maps = MASKED ? p.maps : 1;
+    const float x_out_scale = MASKED ? p.out_scale : 1.f;
+    float* const x_out_f32 = MASKED ? p.out_f32 : nullptr;
     constexpr int STAGES = S::STAGES, SCORE_BUFFERS = S::SCORE_BUFFERS, ALL_BUFFERS = WGS * S::SCORE_BUFFERS;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t q_full, k_full[STAGES], v_full[STAGES], kv_empty[STAGES], s_full[ALL_BUFFERS], p_full[ALL_BUFFERS], o_done[ALL_BUFFERS];
@@ -327,8 +336,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const int u_tile = p.num_tiles - 1 - u / (p.max_parts * p.num_heads);
                 const int u_t0 = p.tiles[u_tile * 3 + 1], u_count = p.tiles[u_tile * 3 + 2];
                 const int u_lo = p.positions[u_t0], u_hi = u_lo + u_count - 1;
-                const int u_first = first_visible(p, u_lo);
-                const int u_tiles = kept_tiles_of(p, u_first / BN) + u_hi / BN - u_first / BN + 1;
+                const int u_first = first_visible<MASKED>(p, u_lo);
+                const int u_tiles = kept_tiles_of<MASKED>(p, u_first / BN) + u_hi / BN - u_first / BN + 1;
                 if (u % p.max_parts < min(p.max_parts, (u_tiles + p.part_tiles - 1) / p.part_tiles)) break;
             }
             unit_slot[round & 1] = u;
@@ -339,12 +348,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int part = unit % p.max_parts;
         const int h = (unit / p.max_parts) % p.num_heads;
         const int tile = p.num_tiles - 1 - unit / (p.max_parts * p.num_heads);
-        const int kvh = (h / p.maps) / (p.num_heads / p.num_kv_heads) * p.maps + h % p.maps;
+        const int kvh = (h / x_maps) / (p.num_heads / p.num_kv_heads) * x_maps + h % x_maps;
         const int seq = p.tiles[tile * 3], t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
         const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;        // positions in a tile are consecutive
-        const int first = first_visible(p, pos_lo);
+        const int first = first_visible<MASKED>(p, pos_lo);
         // the key tiles of this query tile in walking order (kept tiles, then from the first visible key's), and this unit's part of them
-        const int all_lo = first / BN, kept = kept_tiles_of(p, all_lo), all_tiles = kept + pos_hi / BN - all_lo + 1;
+        const int all_lo = first / BN, kept = kept_tiles_of<MASKED>(p, all_lo), all_tiles = kept + pos_hi / BN - all_lo + 1;
         const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
         const int part_begin = (int)((long long)all_tiles * part / parts), part_end = (int)((long long)all_tiles * (part + 1) / parts);
         const int ntiles = part_end - part_begin;
@@ -379,7 +388,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // the cache maps.  A piece outside the visible keys reads the last page.
             auto entry_of = [&](int f) {
                 const int kpos0 = tile_of(f / pieces) * BN + (f % pieces) * p.piece_rows;
-                if (f / pieces >= ntiles || kpos0 > pos_hi || (kpos0 + p.piece_rows - 1 < first && kpos0 >= p.keep_first)) return p.num_pages - 1;
+                if (f / pieces >= ntiles || kpos0 > pos_hi || (kpos0 + p.piece_rows - 1 < first && kpos0 >= x_keep)) return p.num_pages - 1;
                 return __ldg(table + kpos0 / p.page_size);
             };
             auto row_of = [&](int page, int f) {
@@ -492,7 +501,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const bool valid = row < count;
             const int qpos = pos_lo + row;
             const int warp_lo = pos_lo + quad * 32, warp_hi = pos_lo + min(count - 1, quad * 32 + 31);
-            const int warp_first = first_visible(p, warp_lo), row_first = first_visible(p, qpos);
+            const int warp_first = first_visible<MASKED>(p, warp_lo), row_first = first_visible<MASKED>(p, qpos);
             const bool warp_has_rows = quad * 32 < count;
             const float scale_log2 = p.scale * 1.4426950408889634f;
             const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -512,7 +521,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 STAMP(1)
                 const int key_base = tile_of(j) * BN;
                 // a key tile that lies wholly behind or before this warp's rows contributes nothing (kept first keys are never before them)
-                const bool skip = !warp_has_rows || key_base > warp_hi || (key_base + BN - 1 < warp_first && key_base >= p.keep_first);
+                const bool skip = !warp_has_rows || key_base > warp_hi || (key_base + BN - 1 < warp_first && key_base >= x_keep);
                 float c = 1.f, ref = 0.f;
                 float s[64];
                 if (!skip) {
@@ -530,13 +539,13 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     STAMP(2)
                     // only a tile that crosses the diagonal, the window's far edge or the end of the portion needs limits
                     // (also a tile with kept first keys, and one in which a chunk of some row of the warp begins)
-                    const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count || key_base < first_visible(p, warp_lo + 31) ||
-                                        key_base < p.keep_first;
+                    const bool limits = key_base + BN - 1 > warp_lo || quad * 32 + 31 >= count || key_base < first_visible<MASKED>(p, warp_lo + 31) ||
+                                        key_base < x_keep;
                     if (limits) {
 #pragma unroll
                         for (int e = 0; e < 64; ++e) {
                             const int kpos = key_base + e;
-                            const bool see = valid && kpos <= qpos && (kpos >= row_first || kpos < p.keep_first);
+                            const bool see = valid && kpos <= qpos && (kpos >= row_first || kpos < x_keep);
                             if (!see) s[e] = -INFINITY;
                         }
                     }
@@ -674,10 +683,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 // the second group's rows are with the first
             } else if (ok && parts == 1) {
                 tc_fence_after();
-                const float inv = norm_with_sink(m, l, sink_of(p, h)) * p.out_scale;
+                const float inv = norm_with_sink(m, l, sink_of<MASKED>(p, h)) * x_out_scale;
                 const size_t at = (size_t)(t0 + row) * p.ldo + (size_t)h * HD;
                 uint4* dst = reinterpret_cast<uint4*>(p.out + at);
-                float4* dst32 = reinterpret_cast<float4*>(p.out_f32 + at);
+                float4* dst32 = reinterpret_cast<float4*>(x_out_f32 + at);
 #pragma unroll
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     float o[32];
@@ -688,7 +697,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = o[8 * ch + e] * inv;
-                            if (p.out_f32) {
+                            if (x_out_f32) {
                                 dst32[c0 / 4 + 2 * ch] = make_float4(v[0], v[1], v[2], v[3]);
                                 dst32[c0 / 4 + 2 * ch + 1] = make_float4(v[4], v[5], v[6], v[7]);
                             } else {
@@ -747,15 +756,17 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // Adds up the parts of the query tiles whose key ranges were cut: one CTA per (query tile, head), a thread per
 // (row, 16 columns); every part's numbers are requested before the first is used.
 constexpr int MERGE_MAX_PARTS = 8;
-template <int HD>
+template <int HD, bool MASKED>
 __global__ void __launch_bounds__(256)
 attention_merge_parts_kernel(const Params p) {
+    const float x_out_scale = MASKED ? p.out_scale : 1.f;
+    float* const x_out_f32 = MASKED ? p.out_f32 : nullptr;
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int tile = blockIdx.x, h = blockIdx.y;
     const int t0 = p.tiles[tile * 3 + 1], count = p.tiles[tile * 3 + 2];
     const int pos_lo = p.positions[t0], pos_hi = pos_lo + count - 1;
-    const int first = first_visible(p, pos_lo);
-    const int all_tiles = kept_tiles_of(p, first / BN) + pos_hi / BN - first / BN + 1;
+    const int first = first_visible<MASKED>(p, pos_lo);
+    const int all_tiles = kept_tiles_of<MASKED>(p, first / BN) + pos_hi / BN - first / BN + 1;
     const int parts = min(p.max_parts, (all_tiles + p.part_tiles - 1) / p.part_tiles);
     if (parts <= 1) return;
     const size_t slot0 = ((size_t)tile * p.num_heads + h) * p.max_parts;
@@ -783,7 +794,7 @@ attention_merge_parts_kernel(const Params p) {
             w[i] = ml[i].x == -INFINITY ? 0.f : exp2f(ml[i].x - big);                     // -inf: that part saw no key of this row
             total += w[i] * ml[i].y;
         }
-        const float inv = norm_with_sink(big, total, sink_of(p, h)) * p.out_scale;
+        const float inv = norm_with_sink(big, total, sink_of<MASKED>(p, h)) * x_out_scale;
         float acc[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) acc[e] = 0.f;
@@ -797,8 +808,8 @@ attention_merge_parts_kernel(const Params p) {
                 acc[4 * e + 3] = fmaf(w[i], v[i][e].w, acc[4 * e + 3]);
             }
         }
-        if (p.out_f32) {
-            float4* dst32 = reinterpret_cast<float4*>(p.out_f32 + (size_t)(t0 + row) * p.ldo + (size_t)h * HD + c0);
+        if (x_out_f32) {
+            float4* dst32 = reinterpret_cast<float4*>(x_out_f32 + (size_t)(t0 + row) * p.ldo + (size_t)h * HD + c0);
 #pragma unroll
             for (int e = 0; e < 4; ++e) dst32[e] = make_float4(acc[4 * e] * inv, acc[4 * e + 1] * inv, acc[4 * e + 2] * inv, acc[4 * e + 3] * inv);
             continue;
@@ -823,18 +834,18 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
-template <int HD, int WGS>
+template <int HD, int WGS, bool MASKED>
 int launch(cudaStream_t stream, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const Params& p, int sm_count) {
     using S = Shape<HD, WGS>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, WGS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tcgen05_kernel<HD, WGS, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const long long units = (long long)p.num_tiles * p.num_heads * p.max_parts, places = (long long)S::CTAS_PER_SM * sm_count;
     const int ctas = (int)(units < places ? units : places);
-    attention_prefill_tcgen05_kernel<HD, WGS><<<ctas, S::THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
+    attention_prefill_tcgen05_kernel<HD, WGS, MASKED><<<ctas, S::THREADS, S::SMEM_BYTES, stream>>>(map_q, map_k, map_v, p);
     return eg_launch_status();
 }
 
@@ -918,8 +929,11 @@ static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, lon
     static const int asked = getenv("EASY_GPT_PREFILL_GROUPS") ? atoi(getenv("EASY_GPT_PREFILL_GROUPS")) : 0;
     const int groups = asked == 1 || asked == 2 ? asked : eg_attention_prefill_groups(head_dim);
     int code;
-    if (groups == 1) code = head_dim == 64 ? launch<64, 1>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 1>(stream, map_q, map_k, map_v, p, sm_count);
-    else code = head_dim == 64 ? launch<64, 2>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 2>(stream, map_q, map_k, map_v, p, sm_count);
+    const bool masked = extras != nullptr;
+    if (groups == 1 && masked) code = head_dim == 64 ? launch<64, 1, true>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 1, true>(stream, map_q, map_k, map_v, p, sm_count);
+    else if (groups == 1) code = head_dim == 64 ? launch<64, 1, false>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 1, false>(stream, map_q, map_k, map_v, p, sm_count);
+    else if (masked) code = head_dim == 64 ? launch<64, 2, true>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 2, true>(stream, map_q, map_k, map_v, p, sm_count);
+    else code = head_dim == 64 ? launch<64, 2, false>(stream, map_q, map_k, map_v, p, sm_count) : launch<128, 2, false>(stream, map_q, map_k, map_v, p, sm_count);
     if (code || max_parts == 1) return code;
     // the parts are added up behind the main kernel (launched early: it waits for it by itself)
     cudaLaunchConfig_t cfg = {};
@@ -931,8 +945,11 @@ static int attention_prefill_tcgen05_any(cudaStream_t stream, const void* q, lon
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return (int)(head_dim == 64 ? cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<64>, p)
-                                : cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<128>, p));
+    if (masked)
+        return (int)(head_dim == 64 ? cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<64, true>, p)
+                                    : cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<128, true>, p));
+    return (int)(head_dim == 64 ? cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<64, false>, p)
+                                : cudaLaunchKernelEx(&cfg, attention_merge_parts_kernel<128, false>, p));
 }
 
 EG_API int eg_attention_prefill_tcgen05(cudaStream_t stream, const void* q, long long ldq, int total_tokens, const void* k_cache,
